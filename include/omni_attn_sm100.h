@@ -1,0 +1,120 @@
+/* C ABI of the B200 (sm_100a) omni-attention forward library, libomni_attn_sm100.so.
+ *
+ * Plain pointers and sizes only; no torch types. Every function returns 0 on success or a negative
+ * OMNI_ERR_* code, never throws, allocates no device memory and keeps no reference to its
+ * arguments after it returns. All work is enqueued on `cuda_stream` (a cudaStream_t; NULL = the
+ * legacy default stream, which is what the reference's launchers use) and is asynchronous.
+ *
+ * The entry points replace the reference's host launchers
+ *   omni-attn-mma/mma/omni_attn_shared_kv.cu:693-1009   omni_attn_mma_stages_split_q_shared_kv
+ *   omni-attn-mma/mma/omni_attn_swizzle.cu:721-1036     ..._shared_kv_swizzle
+ *   omni-attn-mma/mma/omni_attn_preftech.cu:636-930     omni_attn_preftech_kernel
+ *   omni-attn-mma/mma/omni_attn_cp_async.cu:300-467     omni_attn_cp_async
+ *   omni-attn-mma/mma/attn_naive.cu:305-408             omni_attn_simple_kernel
+ * whose 13 tensor/int arguments (omni-attn-mma/pybind/omni_attn.cc:46-56) map one to one onto
+ * the pointer/size arguments below.
+ */
+#ifndef OMNI_ATTN_SM100_H_
+#define OMNI_ATTN_SM100_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OMNI_ATTN_ABI_VERSION 1
+
+/* dtype argument */
+#define OMNI_DTYPE_F16 0
+#define OMNI_DTYPE_BF16 1
+
+/* Block types, as stored in block_mask_types (omni-attn-mma/omni_attn_torch.py:30-41). */
+#define OMNI_BLOCK_MASKED 0
+#define OMNI_BLOCK_CAUSAL 1
+#define OMNI_BLOCK_FULL 2
+#define OMNI_BLOCK_PARTIAL 3
+
+/* Error codes. The first group mirrors the reference launchers' std::runtime_error checks
+ * (omni-attn-mma/mma/omni_attn_shared_kv.cu:701-753). */
+#define OMNI_OK 0
+#define OMNI_ERR_NULL_POINTER (-1)     /* a required pointer is NULL */
+#define OMNI_ERR_DTYPE (-2)            /* dtype is neither fp16 nor bf16 */
+#define OMNI_ERR_HEAD_DIM (-3)         /* head_dim not in {64, 128} (32 is accepted by the reference, not built here) */
+#define OMNI_ERR_BLOCK_SIZE (-4)       /* q_block/kv_block differ or are not 128 (64 is accepted by the reference, not built here) */
+#define OMNI_ERR_SEQLEN (-5)           /* seqlen_padded not a positive multiple of the block, or seqlen_orig outside (0, seqlen_padded] */
+#define OMNI_ERR_SHAPE (-6)            /* B, H or max_blocks not positive, or B*H*seqlen too large for 32-bit tile coordinates */
+#define OMNI_ERR_PARTIAL (-7)          /* num_partial > 0 without any partial mask pool, or num_partial < 0 */
+#define OMNI_ERR_TOO_LONG (-8)         /* more KV blocks per sequence than the kernel's tables hold (1024 blocks = 131072 tokens) */
+#define OMNI_ERR_ALIGNMENT (-9)        /* q/k/v/o (or a partial mask pool) not 16-byte aligned */
+#define OMNI_ERR_CUDA (-10)            /* a CUDA runtime/driver call failed; see omni_attn_last_cuda_error() */
+#define OMNI_ERR_NO_DRIVER_ENTRY (-11) /* cuTensorMapEncodeTiled is not available from the driver */
+
+/* Values a kernel can leave in *device_status (0 = clean run). Low byte = kind, upper bits = the
+ * place in the kernel that gave up. */
+#define OMNI_STATUS_WAIT_TIMEOUT 1 /* a bounded mbarrier wait ran out; the output is not valid */
+#define OMNI_STATUS_BAD_INDEX 2    /* a kv_indices entry was outside [0, seqlen_padded/128); it was skipped */
+
+/* Forward pass with the warp-specialised kernel.
+ *
+ *  q, k, v           [B, H, seqlen_padded, head_dim], contiguous, 16-bit (dtype), device memory
+ *  o                 same shape and dtype, written in place (rows >= seqlen_orig are zeroed)
+ *  lse_or_null       [B, H, seqlen_padded] fp32: natural-log sum of exp of the scaled, masked
+ *                    scores of each row (-inf for a row that attends nothing), or NULL.
+ *                    The reference has no such output.
+ *  kv_num_blocks     [B, H, nq] int32, nq = seqlen_padded / 128
+ *  kv_indices        [B, H, nq, max_blocks] int32; the first kv_num_blocks entries are used
+ *  block_mask_types  [B, H, nq, max_blocks] int32 (OMNI_BLOCK_*)
+ *  partial_idx_or_null   [B, H, nq, max_blocks] int32 index into the partial pool (-1 = none), or NULL
+ *  partial_bool_or_null  [num_partial, 128, 128] one byte per element, non-zero = attend (the
+ *                        reference's torch.bool tensor), or NULL
+ *  partial_bits_or_null  [num_partial, 128, 4] uint32, bit (c % 32) of word c / 32 of row r = attend;
+ *                        produced by omni_attn_pack_partial_masks_sm100. Used in preference to
+ *                        the byte form when both are given.
+ *  scale             softmax scale; <= 0 selects 1/sqrt(head_dim), the reference's fixed choice
+ *                    (omni-attn-mma/mma/omni_attn_shared_kv.cu:62)
+ *  device_status_or_null  one int32 in device memory the kernel may set to an OMNI_STATUS_* value;
+ *                    the caller zeroes it beforehand and reads it after synchronising.
+ *
+ * A PARTIAL entry whose index is negative or >= num_partial (or any PARTIAL entry when no pool is
+ * given) is treated as CAUSAL, as the reference's dense expansion does
+ * (omni-attn-mma/omni_attn_torch.py:140-143). CAUSAL compares absolute positions.
+ */
+int omni_attn_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* lse_or_null,
+                        const int32_t* kv_num_blocks, const int32_t* kv_indices,
+                        const int32_t* block_mask_types, const int32_t* partial_idx_or_null,
+                        const uint8_t* partial_bool_or_null, const uint32_t* partial_bits_or_null,
+                        int B, int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block,
+                        int kv_block, int max_blocks, int num_partial, int dtype, float scale,
+                        void* cuda_stream, int32_t* device_status_or_null);
+
+/* Same contract, computed by the plain one-tile-per-CTA kernel. It takes the place of the
+ * reference's correctness-first kernel (omni-attn-mma/mma/attn_naive.cu:305-408). */
+int omni_attn_fwd_simple_sm100(const void* q, const void* k, const void* v, void* o,
+                               float* lse_or_null, const int32_t* kv_num_blocks,
+                               const int32_t* kv_indices, const int32_t* block_mask_types,
+                               const int32_t* partial_idx_or_null,
+                               const uint8_t* partial_bool_or_null,
+                               const uint32_t* partial_bits_or_null, int B, int H,
+                               int seqlen_padded, int seqlen_orig, int head_dim, int q_block,
+                               int kv_block, int max_blocks, int num_partial, int dtype, float scale,
+                               void* cuda_stream, int32_t* device_status_or_null);
+
+/* Packs the reference's byte-per-element partial masks ([num_partial,128,128], built by
+ * build_partial_block_data, omni-attn-mma/omni_attn_torch.py:148-205) into one bit per element
+ * ([num_partial,128,4] uint32). Both buffers are device memory owned by the caller. */
+int omni_attn_pack_partial_masks_sm100(const uint8_t* partial_bool, uint32_t* partial_bits,
+                                       int num_partial, void* cuda_stream);
+
+/* Text for an OMNI_ERR_* code; the pointer is static storage. */
+const char* omni_attn_error_string(int code);
+
+/* The cudaError_t (as int) of the most recent failing CUDA call on this thread, 0 if none. */
+int omni_attn_last_cuda_error(void);
+
+int omni_attn_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OMNI_ATTN_SM100_H_ */

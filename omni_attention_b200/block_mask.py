@@ -1,0 +1,348 @@
+"""Block-mask metadata of omni-attention: the same container and type codes as the reference's
+operator surface, with vectorised builders.
+
+Mirrors (same names, fields and meaning):
+  * ``BlockMaskType``  - omni-attn-mma/omni_attn_torch.py:30-41
+  * ``OmniBlockMask``  - omni-attn-mma/omni_attn_torch.py:48-145 (fields, ``num_q_blocks``, ``shape``,
+    ``to_dense_mask``)
+  * ``build_partial_block_data`` - omni-attn-mma/omni_attn_torch.py:148-205
+  * ``create_causal_omni_block_mask`` - omni-attn-mma/omni_attn_torch.py:1950-2015
+
+The reference builds these with Python loops over every block (and every element for CAUSAL
+blocks); here everything is tensor arithmetic so that 32K-token masks are built in milliseconds,
+and masks that follow the "every query row attends keys 0..limit" pattern of interleaved
+text/image sequences (transfusion_pytorch/transfusion.py:496-515) are classified block by block
+without ever materialising an N x N tensor.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from enum import IntEnum
+from typing import Optional, Sequence, Tuple
+
+import torch
+from torch import Tensor
+
+
+class BlockMaskType(IntEnum):
+    MASKED = 0   # block not visited
+    CAUSAL = 1   # key position <= query position (absolute positions)
+    FULL = 2     # every element attends
+    PARTIAL = 3  # per-element mask from the partial pool
+
+
+@dataclass
+class OmniBlockMask:
+    """Block-sparse attention mask.
+
+    kv_num_blocks     [B, H, nq]              number of listed KV blocks per Q block
+    kv_indices        [B, H, nq, max_blocks]  listed KV block ids (first kv_num_blocks valid)
+    block_mask_types  [B, H, nq, max_blocks]  BlockMaskType per listed block
+    q_len, kv_len     padded lengths (multiples of the block sizes)
+    partial_block_mask_indices  [B, H, nq, max_blocks] index into the pool, -1 = none
+    partial_block_masks         [P, Q_BLOCK_SIZE, KV_BLOCK_SIZE] bool, True = attend
+    """
+
+    kv_num_blocks: Tensor
+    kv_indices: Tensor
+    block_mask_types: Tensor
+    q_len: int
+    kv_len: int
+    Q_BLOCK_SIZE: int = 128
+    KV_BLOCK_SIZE: int = 128
+    partial_block_mask_indices: Optional[Tensor] = None
+    partial_block_masks: Optional[Tensor] = None
+    # Device-side copies and the bit-packed partial pool, filled lazily by the operator.
+    _cache: dict = field(default_factory=dict, repr=False, compare=False)
+
+    @property
+    def num_q_blocks(self) -> int:
+        return (self.q_len + self.Q_BLOCK_SIZE - 1) // self.Q_BLOCK_SIZE
+
+    @property
+    def num_kv_blocks(self) -> int:
+        return (self.kv_len + self.KV_BLOCK_SIZE - 1) // self.KV_BLOCK_SIZE
+
+    @property
+    def device(self) -> torch.device:
+        return self.kv_num_blocks.device
+
+    @property
+    def shape(self) -> Tuple[int, int, int, int]:
+        B, H, _ = self.kv_num_blocks.shape
+        return (B, H, self.q_len, self.kv_len)
+
+    def to(self, device) -> "OmniBlockMask":
+        mv = lambda t: None if t is None else t.to(device)
+        return OmniBlockMask(
+            mv(self.kv_num_blocks), mv(self.kv_indices), mv(self.block_mask_types), self.q_len,
+            self.kv_len, self.Q_BLOCK_SIZE, self.KV_BLOCK_SIZE, mv(self.partial_block_mask_indices),
+            mv(self.partial_block_masks))
+
+    def slice_heads(self, start: int, stop: int) -> "OmniBlockMask":
+        """Mask of the flattened (batch*head) range [start, stop), as a [1, stop-start] batch.
+
+        This is the unit multi-GPU sharding works in: every (batch, head) pair is independent.
+        The partial pool is shared, not re-indexed.
+        """
+        B, H, nq = self.kv_num_blocks.shape
+        fl = lambda t: None if t is None else t.reshape(B * H, *t.shape[2:])[start:stop].unsqueeze(0)
+        return OmniBlockMask(
+            fl(self.kv_num_blocks), fl(self.kv_indices), fl(self.block_mask_types), self.q_len,
+            self.kv_len, self.Q_BLOCK_SIZE, self.KV_BLOCK_SIZE, fl(self.partial_block_mask_indices),
+            self.partial_block_masks)
+
+    def visited_blocks(self) -> int:
+        """Listed entries that are actually computed (type FULL, CAUSAL or PARTIAL)."""
+        nb = self.kv_num_blocks.long().clamp(0, self.kv_indices.shape[-1])
+        pos = torch.arange(self.kv_indices.shape[-1], device=self.device)
+        listed = pos < nb.unsqueeze(-1)
+        t = self.block_mask_types
+        return int((listed & (t >= BlockMaskType.CAUSAL) & (t <= BlockMaskType.PARTIAL)).sum().item())
+
+    def sparsity(self) -> float:
+        """Percentage of (Q block, KV block) pairs that are not listed."""
+        B, H, nq = self.kv_num_blocks.shape
+        total = B * H * nq * self.num_kv_blocks
+        return 100.0 * (1.0 - float(self.kv_num_blocks.sum().item()) / total)
+
+    def to_dense_mask(self) -> Tensor:
+        """Boolean [B, H, q_len, kv_len], True = attend."""
+        return dense_mask_from_blocks(self)
+
+
+def dense_mask_from_blocks(bm: OmniBlockMask, bh_range: Optional[Tuple[int, int]] = None) -> Tensor:
+    """Expand listed blocks to a dense boolean mask (optionally only a flattened batch*head range,
+    returned as [n, q_len, kv_len]).
+
+    Semantics of omni-attn-mma/omni_attn_torch.py:89-145: FULL sets the block; CAUSAL sets key <=
+    query by absolute position; PARTIAL copies its pool entry, or falls back to CAUSAL when there is
+    no usable pool entry; MASKED and unlisted blocks stay False.
+    """
+    B, H, nq, mb = bm.kv_indices.shape
+    Bq, Bk = bm.Q_BLOCK_SIZE, bm.KV_BLOCK_SIZE
+    nk = bm.num_kv_blocks
+    dev = bm.device
+    lo, hi = (0, B * H) if bh_range is None else bh_range
+    n = hi - lo
+    flat = lambda t: t.reshape(B * H, *t.shape[2:])[lo:hi]
+    nb = flat(bm.kv_num_blocks).long().clamp(0, mb)
+    idx = flat(bm.kv_indices).long()
+    typ = flat(bm.block_mask_types).long()
+    listed = torch.arange(mb, device=dev) < nb.unsqueeze(-1)
+    listed &= (idx >= 0) & (idx < nk)
+    pidx = None
+    if bm.partial_block_mask_indices is not None and bm.partial_block_masks is not None:
+        pidx = flat(bm.partial_block_mask_indices).long()
+        P = bm.partial_block_masks.shape[0]
+        usable = (pidx >= 0) & (pidx < P)
+    else:
+        usable = torch.zeros_like(listed)
+    is_partial = listed & (typ == BlockMaskType.PARTIAL) & usable
+    is_causal = listed & ((typ == BlockMaskType.CAUSAL) | ((typ == BlockMaskType.PARTIAL) & ~usable))
+    is_full = listed & (typ == BlockMaskType.FULL)
+
+    # block-level grids [n, nq, nk]; a later list entry for the same block overrides nothing
+    # here because FULL/CAUSAL only ever add and PARTIAL entries are written last.
+    blocks = torch.zeros(n, nq, Bq, nk, Bk, dtype=torch.bool, device=dev)
+    qpos = (torch.arange(nq, device=dev) * Bq).view(nq, 1, 1, 1) + torch.arange(Bq, device=dev).view(1, Bq, 1, 1)
+    kpos = (torch.arange(nk, device=dev) * Bk).view(1, 1, nk, 1) + torch.arange(Bk, device=dev).view(1, 1, 1, Bk)
+    causal_pat = kpos <= qpos  # [nq, Bq, nk, Bk]
+
+    def block_grid(sel: Tensor) -> Tensor:
+        g = torch.zeros(n, nq, nk, dtype=torch.bool, device=dev)
+        i0, i1, i2 = sel.nonzero(as_tuple=True)
+        g[i0, i1, idx[i0, i1, i2]] = True
+        return g
+
+    blocks |= block_grid(is_full).view(n, nq, 1, nk, 1)
+    blocks |= block_grid(is_causal).view(n, nq, 1, nk, 1) & causal_pat.unsqueeze(0)
+    if pidx is not None and bool(is_partial.any()):
+        i0, i1, i2 = is_partial.nonzero(as_tuple=True)
+        tiles = bm.partial_block_masks[pidx[i0, i1, i2]].to(torch.bool)  # [m, Bq, Bk]
+        blocks[i0, i1, :, idx[i0, i1, i2], :] = tiles
+    dense = blocks.view(n, nq * Bq, nk * Bk)[:, : bm.q_len, : bm.kv_len]
+    if bh_range is None:
+        return dense.reshape(B, H, bm.q_len, bm.kv_len)
+    return dense
+
+
+def build_partial_block_data(block_mask: OmniBlockMask, dense_mask: Tensor) -> Tuple[Tensor, Tensor]:
+    """Per-element masks of the PARTIAL blocks, cut out of ``dense_mask`` [B, H, q, kv].
+
+    Returns ``(partial_block_mask_indices, partial_block_masks)`` in the reference's format and
+    order (pool entries numbered in (b, h, q_block, list position) order, one entry per listed
+    PARTIAL block, no sharing), omni-attn-mma/omni_attn_torch.py:148-205.
+    """
+    B, H, nq, mb = block_mask.block_mask_types.shape
+    Bq, Bk = block_mask.Q_BLOCK_SIZE, block_mask.KV_BLOCK_SIZE
+    dev = dense_mask.device
+    ql, kl = block_mask.q_len, block_mask.kv_len
+    if dense_mask.shape[2] != ql or dense_mask.shape[3] != kl:
+        padded = torch.zeros(B, H, ql, kl, dtype=dense_mask.dtype, device=dev)
+        a, b = min(dense_mask.shape[2], ql), min(dense_mask.shape[3], kl)
+        padded[:, :, :a, :b] = dense_mask[:, :, :a, :b]
+        dense_mask = padded
+    nqp, nkp = nq * Bq, block_mask.num_kv_blocks * Bk
+    if (ql, kl) != (nqp, nkp):
+        padded = torch.zeros(B, H, nqp, nkp, dtype=dense_mask.dtype, device=dev)
+        padded[:, :, :ql, :kl] = dense_mask
+        dense_mask = padded
+    nb = block_mask.kv_num_blocks.long().clamp(0, mb)
+    listed = torch.arange(mb, device=dev) < nb.unsqueeze(-1)
+    sel = listed & (block_mask.block_mask_types == BlockMaskType.PARTIAL)
+    indices = torch.full((B, H, nq, mb), -1, dtype=torch.int32, device=dev)
+    b_, h_, q_, i_ = sel.nonzero(as_tuple=True)  # row-major order = the reference's loop order
+    m = b_.numel()
+    if m == 0:
+        return indices, torch.empty(0, Bq, Bk, dtype=torch.bool, device=dev)
+    indices[b_, h_, q_, i_] = torch.arange(m, dtype=torch.int32, device=dev)
+    kvb = block_mask.kv_indices[b_, h_, q_, i_].long()
+    tiles = dense_mask.view(B, H, nq, Bq, block_mask.num_kv_blocks, Bk)[b_, h_, q_, :, kvb, :]
+    return indices, tiles.to(torch.bool).contiguous()
+
+
+def create_causal_omni_block_mask(batch: int, nheads: int, q_len: int, kv_len: int,
+                                  Q_BLOCK_SIZE: int = 128, KV_BLOCK_SIZE: int = 128,
+                                  device="cpu") -> OmniBlockMask:
+    """Causal mask: diagonal blocks CAUSAL, blocks below FULL, blocks above not listed
+    (omni-attn-mma/omni_attn_torch.py:1950-2015)."""
+    qp = -(-q_len // Q_BLOCK_SIZE) * Q_BLOCK_SIZE
+    kp = -(-kv_len // KV_BLOCK_SIZE) * KV_BLOCK_SIZE
+    nq, nk = qp // Q_BLOCK_SIZE, kp // KV_BLOCK_SIZE
+    qb = torch.arange(nq, device=device).view(nq, 1)
+    pos = torch.arange(nk, device=device).view(1, nk)
+    listed = pos <= qb
+    idx = torch.where(listed, pos, 0).to(torch.int32)
+    typ = torch.where(listed, torch.where(pos == qb, int(BlockMaskType.CAUSAL), int(BlockMaskType.FULL)),
+                      int(BlockMaskType.MASKED)).to(torch.int32)
+    nb = listed.sum(-1).to(torch.int32)
+    ex = lambda t: t.unsqueeze(0).unsqueeze(0).expand(batch, nheads, *t.shape).contiguous()
+    return OmniBlockMask(ex(nb), ex(idx), ex(typ), qp, kp, Q_BLOCK_SIZE, KV_BLOCK_SIZE)
+
+
+def _pack_lists(grid_type: Tensor) -> Tuple[Tensor, Tensor, Tensor]:
+    """[..., nq, nk] type grid (0 = not listed) -> (kv_num_blocks, kv_indices, block_mask_types) with
+    listed blocks first, ascending, max_blocks = nk."""
+    nk = grid_type.shape[-1]
+    listed = grid_type != 0
+    # stable sort: listed blocks first, ascending block id
+    key = (~listed).to(torch.int32) * nk + torch.arange(nk, device=grid_type.device, dtype=torch.int32)
+    order = key.argsort(dim=-1, stable=True)
+    nb = listed.sum(-1).to(torch.int32)
+    typ = torch.gather(grid_type, -1, order).to(torch.int32)
+    idx = torch.where(typ != 0, order.to(torch.int32), torch.zeros((), dtype=torch.int32, device=grid_type.device))
+    return nb, idx.contiguous(), typ.contiguous()
+
+
+def block_mask_from_row_limits(limits: Tensor, nheads: int, causal_rows: Optional[Tensor] = None,
+                               block: int = 128, share_partial_across_heads: bool = True) -> OmniBlockMask:
+    """Mask where query row q of batch element b attends keys ``0 .. limits[b, q]`` inclusive.
+
+    That is the shape of every interleaved text/image mask: ``limits[q] = q`` on text tokens and the
+    last token of the enclosing span on image tokens (causal | modality rule,
+    transfusion_pytorch/transfusion.py:496-515). Block types follow the reference's derivation from
+    a dense mask (omni-attn-mma/generate_attn_data.py:200-236): all elements set -> FULL; none ->
+    not listed; a diagonal block whose rows are all plain-causal rows -> CAUSAL; anything else ->
+    PARTIAL with its element mask in the pool. ``causal_rows`` [B, N] marks rows that may form a
+    CAUSAL block (default: rows with ``limits == q``).
+
+    Partial pool entries are shared by all heads of a batch element unless
+    ``share_partial_across_heads`` is False, in which case each head gets its own copy exactly as
+    the reference's ``build_partial_block_data`` lays them out. Never builds an N x N tensor.
+    """
+    B, N = limits.shape
+    assert N % block == 0, "sequence length must be a multiple of the block size"
+    dev = limits.device
+    nq = N // block
+    lim = limits.long().view(B, nq, block)
+    if causal_rows is None:
+        causal_rows = limits.long() == torch.arange(N, device=dev)
+    pure = causal_rows.view(B, nq, block).all(-1)  # [B, nq]
+    kstart = torch.arange(nq, device=dev) * block
+    # allowed columns of row (b, qb, r) inside KV block kb: clamp(lim + 1 - kb*block, 0, block)
+    cnt = (lim.unsqueeze(-1) + 1 - kstart.view(1, 1, 1, nq)).clamp(0, block)  # [B, nq, block, nk]
+    all_full = (cnt == block).all(2)
+    all_empty = (cnt == 0).all(2)
+    diag = torch.eye(nq, dtype=torch.bool, device=dev).unsqueeze(0)
+    r = torch.arange(block, device=dev)
+    looks_causal = (cnt == (r + 1).view(1, 1, block, 1)).all(2)  # only ever true on the diagonal
+    grid = torch.full((B, nq, nq), int(BlockMaskType.PARTIAL), dtype=torch.int32, device=dev)
+    grid[diag.expand(B, -1, -1) & looks_causal & pure.unsqueeze(-1)] = int(BlockMaskType.CAUSAL)
+    grid[all_full] = int(BlockMaskType.FULL)
+    grid[all_empty] = int(BlockMaskType.MASKED)
+    nb, idx, typ = _pack_lists(grid)
+
+    is_p = typ == BlockMaskType.PARTIAL  # [B, nq, mb]
+    b_, q_, i_ = is_p.nonzero(as_tuple=True)
+    m = b_.numel()
+    pidx = torch.full((B, nq, nq), -1, dtype=torch.int32, device=dev)
+    pool = torch.empty(0, block, block, dtype=torch.bool, device=dev)
+    if m > 0:
+        pidx[b_, q_, i_] = torch.arange(m, dtype=torch.int32, device=dev)
+        c = cnt[b_, q_, :, idx[b_, q_, i_].long()]  # [m, block] allowed-column counts per row
+        pool = torch.arange(block, device=dev).view(1, 1, block) < c.unsqueeze(-1)
+    exh = lambda t: t.unsqueeze(1).expand(B, nheads, *t.shape[1:]).contiguous()
+    nb, idx, typ, pidx = exh(nb), exh(idx), exh(typ), exh(pidx)
+    if m > 0 and not share_partial_across_heads:
+        # reference layout: entries numbered in (b, h, q_block, position) order, one copy per head
+        per_b = torch.bincount(b_, minlength=B)                      # partial blocks per batch element
+        first = torch.cumsum(per_b, 0) - per_b                       # first shared index of element b
+        local = pidx.long() - first.view(B, 1, 1, 1)                 # index within the batch element
+        base = (first * nheads).view(B, 1, 1, 1) + torch.arange(nheads, device=dev).view(1, nheads, 1, 1) * per_b.view(B, 1, 1, 1)
+        new = torch.where(pidx >= 0, (base + local).to(torch.int32), pidx)
+        order = torch.empty(m * nheads, dtype=torch.long, device=dev)
+        src = pidx[pidx >= 0].long()           # shared index of every (b,h,q,i) entry, row-major
+        order[new[new >= 0].long()] = src
+        pool = pool[order]
+        pidx = new
+    return OmniBlockMask(nb, idx, typ, N, N, block, block, pidx, pool.contiguous())
+
+
+def block_mask_from_dense(dense: Tensor, block: int = 128, causal_ok: Optional[Tensor] = None) -> OmniBlockMask:
+    """Derive an OmniBlockMask from a dense boolean mask [B, H, N, N] (N a multiple of ``block``).
+
+    FULL / not listed / CAUSAL (block equals the absolute-position causal pattern, and, when
+    ``causal_ok`` [nq] is given, only where it allows) / PARTIAL, as in
+    omni-attn-mma/generate_attn_data.py:200-236. For small sizes and tests.
+    """
+    B, H, N, _ = dense.shape
+    nq = N // block
+    dev = dense.device
+    t = dense.view(B, H, nq, block, nq, block).permute(0, 1, 2, 4, 3, 5)  # [B,H,nq,nk,Bq,Bk]
+    all_ = t.all(-1).all(-1)
+    any_ = t.any(-1).any(-1)
+    pos = torch.arange(N, device=dev)
+    causal = (pos.view(1, N) <= pos.view(N, 1)).view(nq, block, nq, block).permute(0, 2, 1, 3)
+    is_c = (t == causal.view(1, 1, nq, nq, block, block)).all(-1).all(-1)
+    if causal_ok is not None:
+        is_c &= causal_ok.view(1, 1, nq, 1).to(dev)
+    grid = torch.full((B, H, nq, nq), int(BlockMaskType.PARTIAL), dtype=torch.int32, device=dev)
+    grid[is_c] = int(BlockMaskType.CAUSAL)
+    grid[all_] = int(BlockMaskType.FULL)
+    grid[~any_] = int(BlockMaskType.MASKED)
+    nb, idx, typ = _pack_lists(grid)
+    bm = OmniBlockMask(nb, idx, typ, N, N, block, block)
+    if bool((typ == BlockMaskType.PARTIAL).any()):
+        bm.partial_block_mask_indices, bm.partial_block_masks = build_partial_block_data(bm, dense)
+    return bm
+
+
+def row_limits_from_modality_positions(seq_len: int, modality_positions: Sequence[Sequence[Tuple[int, int]]],
+                                       device="cpu") -> Tuple[Tensor, Tensor]:
+    """Per-row attention limits for the causal | modality rule.
+
+    ``modality_positions[b]`` lists ``(offset, length)`` of the bidirectional (image) spans of batch
+    element b. Returns ``(limits [B, N], causal_rows [B, N])``: a token inside a span attends
+    through the span's last token, any other token attends causally.
+    """
+    B = len(modality_positions)
+    limits = torch.arange(seq_len, device=device).repeat(B, 1)
+    causal_rows = torch.ones(B, seq_len, dtype=torch.bool, device=device)
+    for b, spans in enumerate(modality_positions):
+        for off, length in spans:
+            lo, hi = max(0, int(off)), min(seq_len, int(off) + int(length))
+            if hi > lo:
+                limits[b, lo:hi] = torch.maximum(limits[b, lo:hi], torch.tensor(hi - 1, device=device))
+                causal_rows[b, lo:hi] = False
+    return limits, causal_rows

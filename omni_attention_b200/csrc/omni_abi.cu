@@ -1,0 +1,212 @@
+// C-ABI layer of libomni_attn_sm100.so: argument validation (the checks of the reference's host
+// launchers, omni-attn-mma/mma/omni_attn_shared_kv.cu:701-753, as error codes instead of
+// exceptions), TMA tensor-map construction and kernel dispatch.
+#include <cmath>
+#include <cstdint>
+
+#include "../../include/omni_attn_sm100.h"
+#include "omni_launch.h"
+
+namespace omni {
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so that the library has no link-time
+// dependency on libcuda (it must load on a machine without a driver for symbol checks).
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    else (void)cudaGetLastError();
+    tried = true;
+  }
+  return fn;
+}
+
+// [rows, head_dim] 16-bit row-major view of one of Q/K/V; box = 128 rows x 64 columns (128 bytes),
+// 128-byte swizzle, which is the layout the UMMA shared-memory descriptors of the kernels expect.
+int make_tile_map(CUtensorMap* tm, const void* base, long long rows, int head_dim, bool bf16) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return OMNI_ERR_NO_DRIVER_ENTRY;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(head_dim) * 2};
+  const cuuint32_t box[2] = {64, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return OMNI_ERR_CUDA;
+  }
+  return OMNI_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int forward(bool simple, const void* q, const void* k, const void* v, void* o, float* lse,
+            const int32_t* kv_num_blocks, const int32_t* kv_indices, const int32_t* types,
+            const int32_t* partial_idx, const uint8_t* partial_bool, const uint32_t* partial_bits, int B,
+            int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block, int kv_block,
+            int max_blocks, int num_partial, int dtype, float scale, void* stream, int32_t* status) {
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || kv_num_blocks == nullptr ||
+      kv_indices == nullptr || types == nullptr) {
+    return OMNI_ERR_NULL_POINTER;
+  }
+  if (dtype != OMNI_DTYPE_F16 && dtype != OMNI_DTYPE_BF16) return OMNI_ERR_DTYPE;
+  if (head_dim != 64 && head_dim != 128) return OMNI_ERR_HEAD_DIM;
+  if (q_block != kBlock || kv_block != kBlock) return OMNI_ERR_BLOCK_SIZE;
+  if (seqlen_padded <= 0 || seqlen_padded % kBlock != 0 || seqlen_orig <= 0 || seqlen_orig > seqlen_padded) {
+    return OMNI_ERR_SEQLEN;
+  }
+  if (B <= 0 || H <= 0 || max_blocks <= 0) return OMNI_ERR_SHAPE;
+  const long long BH = static_cast<long long>(B) * H;
+  const long long rows = BH * seqlen_padded;
+  if (rows >= (1LL << 31) || BH > 65535) return OMNI_ERR_SHAPE;
+  if (num_partial < 0) return OMNI_ERR_PARTIAL;
+  if (num_partial > 0 && partial_bool == nullptr && partial_bits == nullptr) return OMNI_ERR_PARTIAL;
+  const int nq = seqlen_padded / kBlock;
+  if (nq > kMaxKvBlocks) return OMNI_ERR_TOO_LONG;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(partial_bool) ||
+      !aligned16(partial_bits)) {
+    return OMNI_ERR_ALIGNMENT;
+  }
+
+  const bool bf16 = dtype == OMNI_DTYPE_BF16;
+  CUtensorMap tmQ, tmK, tmV;
+  int rc = make_tile_map(&tmQ, q, rows, head_dim, bf16);
+  if (rc != OMNI_OK) return rc;
+  rc = make_tile_map(&tmK, k, rows, head_dim, bf16);
+  if (rc != OMNI_OK) return rc;
+  rc = make_tile_map(&tmV, v, rows, head_dim, bf16);
+  if (rc != OMNI_OK) return rc;
+
+  FwdParams p;
+  p.o = o;
+  p.lse = lse;
+  p.kv_num_blocks = kv_num_blocks;
+  p.kv_indices = kv_indices;
+  p.types = types;
+  p.partial_idx = num_partial > 0 ? partial_idx : nullptr;
+  p.partial_bool = num_partial > 0 ? partial_bool : nullptr;
+  p.partial_bits = num_partial > 0 ? partial_bits : nullptr;
+  p.status = status;
+  p.work_order = nullptr;
+  p.BH = static_cast<int>(BH);
+  p.N = seqlen_padded;
+  p.seqlen_orig = seqlen_orig;
+  p.nq = nq;
+  p.max_blocks = max_blocks;
+  p.num_partial = num_partial;
+  p.scale = scale > 0.f ? scale : 1.f / std::sqrt(static_cast<float>(head_dim));
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = simple ? launch_simple(head_dim, bf16, tmQ, tmK, tmV, p, st)
+                         : launch_ws(head_dim, bf16, tmQ, tmK, tmV, p, st);
+  if (e != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(e);
+    return OMNI_ERR_CUDA;
+  }
+  return OMNI_OK;
+}
+
+// One thread per output word: 32 mask bytes -> 32 bits.
+__global__ void pack_partial_kernel(const uint8_t* __restrict__ src, uint32_t* __restrict__ dst,
+                                    long long n_words) {
+  const long long w = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (w >= n_words) return;
+  const uint4* s = reinterpret_cast<const uint4*>(src + w * 32);
+  const uint4 a = __ldg(s);
+  const uint4 b = __ldg(s + 1);
+  dst[w] = bytes_to_nibble(a.x) | (bytes_to_nibble(a.y) << 4) | (bytes_to_nibble(a.z) << 8) |
+           (bytes_to_nibble(a.w) << 12) | (bytes_to_nibble(b.x) << 16) | (bytes_to_nibble(b.y) << 20) |
+           (bytes_to_nibble(b.z) << 24) | (bytes_to_nibble(b.w) << 28);
+}
+
+}  // namespace
+}  // namespace omni
+
+extern "C" {
+
+int omni_attn_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* lse_or_null,
+                        const int32_t* kv_num_blocks, const int32_t* kv_indices,
+                        const int32_t* block_mask_types, const int32_t* partial_idx_or_null,
+                        const uint8_t* partial_bool_or_null, const uint32_t* partial_bits_or_null,
+                        int B, int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block,
+                        int kv_block, int max_blocks, int num_partial, int dtype, float scale,
+                        void* cuda_stream, int32_t* device_status_or_null) {
+  return omni::forward(false, q, k, v, o, lse_or_null, kv_num_blocks, kv_indices, block_mask_types,
+                       partial_idx_or_null, partial_bool_or_null, partial_bits_or_null, B, H,
+                       seqlen_padded, seqlen_orig, head_dim, q_block, kv_block, max_blocks, num_partial,
+                       dtype, scale, cuda_stream, device_status_or_null);
+}
+
+int omni_attn_fwd_simple_sm100(const void* q, const void* k, const void* v, void* o,
+                               float* lse_or_null, const int32_t* kv_num_blocks,
+                               const int32_t* kv_indices, const int32_t* block_mask_types,
+                               const int32_t* partial_idx_or_null,
+                               const uint8_t* partial_bool_or_null,
+                               const uint32_t* partial_bits_or_null, int B, int H,
+                               int seqlen_padded, int seqlen_orig, int head_dim, int q_block,
+                               int kv_block, int max_blocks, int num_partial, int dtype, float scale,
+                               void* cuda_stream, int32_t* device_status_or_null) {
+  return omni::forward(true, q, k, v, o, lse_or_null, kv_num_blocks, kv_indices, block_mask_types,
+                       partial_idx_or_null, partial_bool_or_null, partial_bits_or_null, B, H,
+                       seqlen_padded, seqlen_orig, head_dim, q_block, kv_block, max_blocks, num_partial,
+                       dtype, scale, cuda_stream, device_status_or_null);
+}
+
+int omni_attn_pack_partial_masks_sm100(const uint8_t* partial_bool, uint32_t* partial_bits,
+                                       int num_partial, void* cuda_stream) {
+  if (num_partial < 0) return OMNI_ERR_PARTIAL;
+  if (num_partial == 0) return OMNI_OK;
+  if (partial_bool == nullptr || partial_bits == nullptr) return OMNI_ERR_NULL_POINTER;
+  if (!omni::aligned16(partial_bool) || !omni::aligned16(partial_bits)) return OMNI_ERR_ALIGNMENT;
+  const long long n_words = static_cast<long long>(num_partial) * omni::kBlock * 4;
+  const int threads = 256;
+  const long long blocks = (n_words + threads - 1) / threads;
+  omni::pack_partial_kernel<<<static_cast<unsigned>(blocks), threads, 0,
+                              static_cast<cudaStream_t>(cuda_stream)>>>(partial_bool, partial_bits, n_words);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    omni::g_last_cuda_error = static_cast<int>(e);
+    return OMNI_ERR_CUDA;
+  }
+  return OMNI_OK;
+}
+
+const char* omni_attn_error_string(int code) {
+  switch (code) {
+    case OMNI_OK: return "ok";
+    case OMNI_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case OMNI_ERR_DTYPE: return "dtype must be fp16 (0) or bf16 (1)";
+    case OMNI_ERR_HEAD_DIM: return "head_dim must be 64 or 128";
+    case OMNI_ERR_BLOCK_SIZE: return "Q_BLOCK_SIZE and KV_BLOCK_SIZE must both be 128";
+    case OMNI_ERR_SEQLEN: return "seqlen_padded must be a positive multiple of 128 and 0 < seqlen_orig <= seqlen_padded";
+    case OMNI_ERR_SHAPE: return "B, H, max_blocks must be positive, B*H <= 65535 and B*H*seqlen < 2^31";
+    case OMNI_ERR_PARTIAL: return "num_partial is negative, or positive without a partial mask pool";
+    case OMNI_ERR_TOO_LONG: return "sequence longer than 1024 KV blocks (131072 tokens)";
+    case OMNI_ERR_ALIGNMENT: return "q, k, v, o and the partial mask pools must be 16-byte aligned";
+    case OMNI_ERR_CUDA: return "a CUDA call failed (see omni_attn_last_cuda_error)";
+    case OMNI_ERR_NO_DRIVER_ENTRY: return "cuTensorMapEncodeTiled not available from the CUDA driver";
+    default: return "unknown error code";
+  }
+}
+
+int omni_attn_last_cuda_error(void) { return omni::g_last_cuda_error; }
+
+int omni_attn_abi_version(void) { return OMNI_ATTN_ABI_VERSION; }
+
+}  // extern "C"

@@ -1,0 +1,299 @@
+// Shared device-side pieces of the omni-attention forward kernels: launch parameters, block-list
+// entry resolution (what a listed KV block means for one Q block), per-row allow-bit masks for
+// CAUSAL / PARTIAL / clipped tiles and the register-level online-softmax step.
+//
+// Semantics follow the reference's dense expansion of an OmniBlockMask
+// (omni-attn-mma/omni_attn_torch.py:89-145) and its scalar kernel (omni-attn-mma/mma/attn_naive.cu:95-301):
+//   * CAUSAL compares absolute positions (k_abs <= q_abs), so a CAUSAL entry below the diagonal is
+//     a FULL tile and one above the diagonal contributes nothing;
+//   * a PARTIAL entry without a usable per-element mask falls back to CAUSAL (omni_attn_torch.py:140-143);
+//   * keys at positions >= seqlen_orig are never attended (attn_naive.cu:113);
+//   * entries at index >= kv_num_blocks, MASKED entries and out-of-range block ids are ignored.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx_sm100.cuh"
+
+namespace omni {
+
+constexpr int kBlock = 128;  // Q_BLOCK_SIZE == KV_BLOCK_SIZE == 128 is the only tile shape built.
+
+// Block type codes of the reference (omni_attn_torch.py:30-41).
+constexpr int kTypeMasked = 0;
+constexpr int kTypeCausal = 1;
+constexpr int kTypeFull = 2;
+constexpr int kTypePartial = 3;
+
+// Resolved entry code: bits [1:0] type (0 = not visited), bit 2 = clipped by seqlen_orig,
+// bits [31:3] = index into the partial-mask pool.
+constexpr uint32_t kCodeTypeMask = 3u;
+constexpr uint32_t kCodeClip = 4u;
+
+struct FwdParams {
+  void* o;                        // [BH, N, D] 16-bit
+  float* lse;                     // [BH, N] or null
+  const int32_t* kv_num_blocks;   // [BH, nq]
+  const int32_t* kv_indices;      // [BH, nq, max_blocks]
+  const int32_t* types;           // [BH, nq, max_blocks]
+  const int32_t* partial_idx;     // [BH, nq, max_blocks] or null
+  const uint8_t* partial_bool;    // [P, 128, 128] bytes or null
+  const uint32_t* partial_bits;   // [P, 128, 4] words (bit c of row r = attend) or null
+  int32_t* status;                // device status word or null
+  const int32_t* work_order;      // optional [num_work] CTA -> work-unit permutation, or null
+  int BH;
+  int N;            // padded sequence length (multiple of 128)
+  int seqlen_orig;  // unpadded length
+  int nq;           // N / 128
+  int max_blocks;
+  int num_partial;
+  float scale;       // softmax scale
+  float scale_log2;  // scale * log2(e)
+};
+
+// Resolve entry `i` of the list of (bh, qb). Returns 0 when the entry is not visited.
+__device__ __forceinline__ uint32_t resolve_entry(const FwdParams& p, long long list_base, int i,
+                                                  int qb, int& kvb_out) {
+  const int kvb = __ldg(p.kv_indices + list_base + i);
+  int t = __ldg(p.types + list_base + i);
+  kvb_out = kvb;
+  if (kvb < 0 || kvb >= p.nq) {
+    if (p.status != nullptr) atomicCAS(p.status, 0, kStatusBadIndex);
+    return 0;
+  }
+  if (t <= kTypeMasked || t > kTypePartial) return 0;
+  const int kv_start = kvb * kBlock;
+  if (kv_start >= p.seqlen_orig) return 0;
+  uint32_t pidx = 0;
+  if (t == kTypePartial) {
+    int pi = -1;
+    if (p.partial_idx != nullptr && (p.partial_bool != nullptr || p.partial_bits != nullptr)) {
+      pi = __ldg(p.partial_idx + list_base + i);
+    }
+    if (pi >= 0 && pi < p.num_partial) {
+      pidx = static_cast<uint32_t>(pi);
+    } else {
+      t = kTypeCausal;
+    }
+  }
+  if (t == kTypeCausal) {
+    if (kvb < qb) {
+      t = kTypeFull;
+    } else if (kvb > qb) {
+      return 0;
+    }
+  }
+  const uint32_t clip = (kv_start + kBlock > p.seqlen_orig) ? kCodeClip : 0u;
+  return static_cast<uint32_t>(t) | clip | (pidx << 3);
+}
+
+// Four 0/1 bytes -> 4 bits (byte i -> bit i). Any non-zero byte counts as true.
+__device__ __forceinline__ uint32_t bytes_to_nibble(uint32_t w) {
+  const uint32_t x = __vcmpne4(w, 0u) & 0x01010101u;
+  return ((x * 0x01020408u) >> 24) & 0xFu;
+}
+
+// Load the 128 allow-bits of row `r` of partial tile `pidx` (bit c of word c/32 = attend).
+__device__ __forceinline__ void load_partial_row(const FwdParams& p, uint32_t pidx, int r,
+                                                 uint32_t (&allow)[4]) {
+  if (p.partial_bits != nullptr) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.partial_bits) +
+                          (static_cast<size_t>(pidx) * kBlock + r));
+    allow[0] = v.x; allow[1] = v.y; allow[2] = v.z; allow[3] = v.w;
+  } else {
+    const uint4* src = reinterpret_cast<const uint4*>(
+        p.partial_bool + (static_cast<size_t>(pidx) * kBlock + r) * kBlock);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const uint4 a = __ldg(src + 2 * w);
+      const uint4 b = __ldg(src + 2 * w + 1);
+      allow[w] = bytes_to_nibble(a.x) | (bytes_to_nibble(a.y) << 4) | (bytes_to_nibble(a.z) << 8) |
+                 (bytes_to_nibble(a.w) << 12) | (bytes_to_nibble(b.x) << 16) |
+                 (bytes_to_nibble(b.y) << 20) | (bytes_to_nibble(b.z) << 24) |
+                 (bytes_to_nibble(b.w) << 28);
+    }
+  }
+}
+
+// Allow-bits of row r for a diagonal CAUSAL tile: column c allowed iff c <= r.
+__device__ __forceinline__ void causal_row(int r, uint32_t (&allow)[4]) {
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const int d = r - 32 * w;  // highest allowed bit in this word
+      allow[w] = d >= 31 ? 0xFFFFFFFFu : (d < 0 ? 0u : ((2u << d) - 1u));
+    }
+}
+
+// Keep only columns c < limit (1 <= limit <= 127).
+__device__ __forceinline__ void clip_row(int limit, uint32_t (&allow)[4]) {
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const int d = limit - 1 - 32 * w;
+    allow[w] &= d >= 31 ? 0xFFFFFFFFu : (d < 0 ? 0u : ((2u << d) - 1u));
+  }
+}
+
+// Build the allow-bits of row r for a non-FULL or clipped tile.
+__device__ __forceinline__ void build_allow(const FwdParams& p, uint32_t code, int kvb, int r,
+                                            uint32_t (&allow)[4]) {
+  const uint32_t t = code & kCodeTypeMask;
+  if (t == kTypePartial) {
+    load_partial_row(p, code >> 3, r, allow);
+  } else if (t == kTypeCausal) {
+    causal_row(r, allow);
+  } else {
+    allow[0] = allow[1] = allow[2] = allow[3] = 0xFFFFFFFFu;
+  }
+  if (code & kCodeClip) clip_row(p.seqlen_orig - kvb * kBlock, allow);
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (BF16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  } else {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+
+// Running softmax state of one query row (one thread).
+struct RowState {
+  float m;  // running max of the raw (unscaled) scores the exponentials are taken against
+  float l;  // running sum of exp2((s - m) * scale_log2)
+};
+
+// Read the 128 raw scores of this thread's row from TMEM.
+__device__ __forceinline__ void load_scores(uint32_t taddr_row, float (&s)[128]) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr_row + 32 * c, r);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) s[32 * c + j] = __uint_as_float(r[j]);
+  }
+  tc_wait_ld();
+}
+
+__device__ __forceinline__ void apply_allow(const uint32_t (&allow)[4], float (&s)[128]) {
+#pragma unroll
+  for (int j = 0; j < 128; ++j) {
+    s[j] = ((allow[j >> 5] >> (j & 31)) & 1u) ? s[j] : -INFINITY;
+  }
+}
+
+__device__ __forceinline__ float row_max(const float (&s)[128]) {
+  float a = fmaxf(s[0], s[1]), b = fmaxf(s[2], s[3]), c = fmaxf(s[4], s[5]), d = fmaxf(s[6], s[7]);
+#pragma unroll
+  for (int j = 8; j < 128; j += 8) {
+    a = fmaxf(a, fmaxf(s[j], s[j + 1]));
+    b = fmaxf(b, fmaxf(s[j + 2], s[j + 3]));
+    c = fmaxf(c, fmaxf(s[j + 4], s[j + 5]));
+    d = fmaxf(d, fmaxf(s[j + 6], s[j + 7]));
+  }
+  return fmaxf(fmaxf(a, b), fmaxf(c, d));
+}
+
+// Online-softmax update for one tile. `lazy_log2` > 0 keeps the old reference max while the tile
+// max exceeds it by at most that many powers of two (the exponentials then reach 2^lazy_log2,
+// harmless in fp32 sums and in 16-bit P). Returns the factor the O accumulator must be
+// multiplied by before this tile's P*V is added (1 when the reference max did not move).
+__device__ __forceinline__ float softmax_update(RowState& st, float tile_max, float scale_log2,
+                                                float lazy_log2) {
+  const float m_old = st.m;
+  float m_new = fmaxf(m_old, tile_max);
+  if (lazy_log2 > 0.f && m_old != -INFINITY && (m_new - m_old) * scale_log2 <= lazy_log2) {
+    m_new = m_old;
+  }
+  float alpha = 1.f;
+  if (m_new != m_old) {
+    // m_old == -inf gives exp2(-inf) = 0: nothing accumulated so far survives, which is right.
+    alpha = ex2_approx((m_old - m_new) * scale_log2);
+    st.m = m_new;
+  }
+  return alpha;
+}
+
+// P = exp2((s - m) * scale_log2) for the whole row, packed to 16-bit pairs; returns the row sum of
+// the unrounded exponentials. A row with no allowed key in any tile so far has m = -inf: every s
+// is -inf too and all P are 0.
+template <bool BF16>
+__device__ __forceinline__ float exp_and_pack(const float (&s)[128], float m, float scale_log2,
+                                              uint32_t (&pk)[64]) {
+  const float m_use = (m == -INFINITY) ? 0.f : m;
+  const float neg = -m_use * scale_log2;
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < 64; ++j) {
+    const float p0 = ex2_approx(fmaf(s[2 * j], scale_log2, neg));
+    const float p1 = ex2_approx(fmaf(s[2 * j + 1], scale_log2, neg));
+    sum0 += p0;
+    sum1 += p1;
+    pk[j] = pack2<BF16>(p0, p1);
+  }
+  return sum0 + sum1;
+}
+
+// Write the packed P row (64 words) to TMEM columns [taddr_row, taddr_row + 64).
+__device__ __forceinline__ void store_p(uint32_t taddr_row, const uint32_t (&pk)[64]) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t r[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = pk[32 * c + j];
+    tmem_st32(taddr_row + 32 * c, r);
+  }
+}
+
+// O[row, :] *= alpha in TMEM (D fp32 columns starting at taddr_row).
+template <int D>
+__device__ __forceinline__ void rescale_o(uint32_t taddr_row, float alpha) {
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr_row + 32 * c, r);
+    tc_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+    tmem_st32(taddr_row + 32 * c, r);
+  }
+}
+
+// Final normalisation and store of one output row: O = acc / l (0 when the row attended nothing),
+// LSE = scale * m + ln(l) (-inf when the row attended nothing). `zero_row` forces zeros (padding).
+template <int D, bool BF16>
+__device__ __forceinline__ void store_output_row(uint32_t taddr_row, bool have_acc,
+                                                 const RowState& st, const FwdParams& p,
+                                                 long long row_index, bool zero_row) {
+  const bool empty = zero_row || !have_acc || !(st.l > 0.f);
+  const float inv = empty ? 0.f : 1.f / st.l;
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(p.o) + row_index * (D * 2));
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t r[32];
+    if (have_acc) {  // uniform across the CTA's softmax threads of this tile
+      tmem_ld32(taddr_row + 32 * c, r);
+      tc_wait_ld();
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = 0u;
+    }
+    uint32_t w[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float a = empty ? 0.f : __uint_as_float(r[2 * j]) * inv;
+      const float b = empty ? 0.f : __uint_as_float(r[2 * j + 1]) * inv;
+      w[j] = pack2<BF16>(a, b);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      dst[4 * c + j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    }
+  }
+  if (p.lse != nullptr) {
+    p.lse[row_index] = empty ? -INFINITY : fmaf(st.m, p.scale, __logf(st.l));
+  }
+}
+
+}  // namespace omni

@@ -1,0 +1,211 @@
+"""Host-side operator: ``omni_attention(q, k, v, block_mask)``.
+
+Same contract as the reference's wrappers ``omni_attention_shared_kv`` and siblings
+(omni-attn-mma/omni_attn_torch.py:517-671): ``[B, H, N, D]`` inputs, an ``OmniBlockMask``, output
+``[B, H, N, D]`` sliced back to the unpadded length. Differences, all deliberate:
+  * the input dtype is kept (fp16 or bf16); the reference forces ``.half()`` (:609-611);
+  * ``scale`` is honoured; the reference accepts and drops it (:517-523 vs :652-663);
+  * the launch goes to torch's current stream and nothing synchronises the device (the reference
+    calls ``torch.cuda.synchronize()`` after every launch, :666);
+  * ``return_lse=True`` also returns the log-sum-exp rows;
+  * mask tensors are converted / bit-packed once per mask object and cached on it.
+The call goes through the C ABI of ``libomni_attn_sm100.so`` with raw device pointers. There is no
+CPU or PyTorch fallback: a missing library or a non-CUDA tensor raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from typing import Optional, Tuple, Union
+
+import torch
+from torch import Tensor
+
+from .block_mask import OmniBlockMask
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libomni_attn_sm100.so")
+_lib = None
+
+# symbols include/omni_attn_sm100.h declares
+ABI_SYMBOLS = (
+    "omni_attn_fwd_sm100",
+    "omni_attn_fwd_simple_sm100",
+    "omni_attn_pack_partial_masks_sm100",
+    "omni_attn_error_string",
+    "omni_attn_last_cuda_error",
+    "omni_attn_abi_version",
+)
+
+STATUS_WAIT_TIMEOUT = 1
+STATUS_BAD_INDEX = 2
+
+
+class OmniAttnError(RuntimeError):
+    """A C-ABI call returned an error code, or a kernel reported a bad status."""
+
+
+def load_library() -> ctypes.CDLL:
+    """Load libomni_attn_sm100.so from the package directory (built by ``omni_attention_b200.build``)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            f"{_LIB_PATH} not found: build it with `python -m omni_attention_b200.build` "
+            "(there is no fallback implementation)")
+    lib = ctypes.CDLL(_LIB_PATH)
+    vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    fwd_args = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp] + [i32] * 10 + [f32, vp, vp]
+    for name in ("omni_attn_fwd_sm100", "omni_attn_fwd_simple_sm100"):
+        fn = getattr(lib, name)
+        fn.argtypes = fwd_args
+        fn.restype = i32
+    lib.omni_attn_pack_partial_masks_sm100.argtypes = [vp, vp, i32, vp]
+    lib.omni_attn_pack_partial_masks_sm100.restype = i32
+    lib.omni_attn_error_string.argtypes = [i32]
+    lib.omni_attn_error_string.restype = ctypes.c_char_p
+    lib.omni_attn_last_cuda_error.argtypes = []
+    lib.omni_attn_last_cuda_error.restype = i32
+    lib.omni_attn_abi_version.argtypes = []
+    lib.omni_attn_abi_version.restype = i32
+    _lib = lib
+    return lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        lib = load_library()
+        msg = lib.omni_attn_error_string(rc).decode()
+        extra = f", CUDA error {lib.omni_attn_last_cuda_error()}" if rc == -10 else ""
+        raise OmniAttnError(f"omni_attn: {msg} (code {rc}{extra})")
+
+
+def _ptr(t: Optional[Tensor]) -> Optional[int]:
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def pack_partial_masks(partial_block_masks: Tensor) -> Tensor:
+    """[P, 128, 128] bool (CUDA) -> [P, 128, 4] int32 bit masks, on the current stream."""
+    assert partial_block_masks.is_cuda and partial_block_masks.dtype == torch.bool
+    P = partial_block_masks.shape[0]
+    src = partial_block_masks.contiguous()
+    bits = torch.empty(P, 128, 4, dtype=torch.int32, device=src.device)
+    if P > 0:
+        with torch.cuda.device(src.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            _check(load_library().omni_attn_pack_partial_masks_sm100(src.data_ptr(), bits.data_ptr(), P, stream))
+    return bits
+
+
+def _device_mask(bm: OmniBlockMask, device: torch.device, pack_bits: bool) -> dict:
+    """int32 contiguous copies of the mask tensors on ``device`` (+ bit-packed pool), cached on the mask."""
+    key = (str(device), pack_bits)
+    hit = bm._cache.get(key)
+    if hit is not None:
+        return hit
+    cv = lambda t: t.to(device=device, dtype=torch.int32).contiguous()
+    d = {"nb": cv(bm.kv_num_blocks), "idx": cv(bm.kv_indices), "typ": cv(bm.block_mask_types),
+         "pidx": None, "pbool": None, "pbits": None, "num_partial": 0}
+    if bm.partial_block_mask_indices is not None and bm.partial_block_masks is not None:
+        d["pidx"] = cv(bm.partial_block_mask_indices)
+        pool = bm.partial_block_masks.to(device=device, dtype=torch.bool).contiguous()
+        d["num_partial"] = int(pool.shape[0])
+        if pool.shape[0] > 0:
+            if pack_bits:
+                d["pbits"] = pack_partial_masks(pool)
+            else:
+                d["pbool"] = pool
+    bm._cache[key] = d
+    return d
+
+
+def omni_attention_forward_out(q: Tensor, k: Tensor, v: Tensor, out: Tensor, block_mask: OmniBlockMask,
+                               seqlen_orig: int, scale: Optional[float] = None, lse: Optional[Tensor] = None,
+                               status: Optional[Tensor] = None, kernel: str = "ws", pack_bits: bool = True) -> None:
+    """Launch the forward on padded, contiguous CUDA tensors; writes ``out`` (and ``lse``) in place."""
+    if not (q.is_cuda and k.is_cuda and v.is_cuda and out.is_cuda):
+        raise OmniAttnError("omni_attention needs CUDA tensors (there is no CPU path)")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise OmniAttnError(f"unsupported dtype {q.dtype}: fp16 or bf16")
+    for t in (k, v, out):
+        if t.dtype != q.dtype or t.shape != q.shape:
+            raise OmniAttnError("q, k, v, out must share dtype and shape (Q_len == KV_len)")
+    for t in (q, k, v, out):
+        if not t.is_contiguous():
+            raise OmniAttnError("q, k, v, out must be contiguous")
+    B, H, N, D = q.shape
+    m = _device_mask(block_mask, q.device, pack_bits)
+    nq = N // block_mask.Q_BLOCK_SIZE if block_mask.Q_BLOCK_SIZE else 0
+    if tuple(m["nb"].shape) != (B, H, nq):
+        raise OmniAttnError(f"kv_num_blocks shape {tuple(m['nb'].shape)} != {(B, H, nq)}")
+    if tuple(m["idx"].shape[:3]) != (B, H, nq) or m["typ"].shape != m["idx"].shape:
+        raise OmniAttnError("kv_indices / block_mask_types shape mismatch")
+    if m["pidx"] is not None and m["pidx"].shape != m["idx"].shape:
+        raise OmniAttnError("partial_block_mask_indices shape mismatch")
+    if lse is not None and (lse.dtype != torch.float32 or lse.numel() != B * H * N or not lse.is_contiguous()):
+        raise OmniAttnError("lse must be contiguous float32 [B, H, N]")
+    lib = load_library()
+    fn = lib.omni_attn_fwd_sm100 if kernel == "ws" else lib.omni_attn_fwd_simple_sm100
+    if kernel not in ("ws", "simple"):
+        raise OmniAttnError(f"unknown kernel {kernel!r}")
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _ptr(lse), m["nb"].data_ptr(),
+                m["idx"].data_ptr(), m["typ"].data_ptr(), _ptr(m["pidx"]), _ptr(m["pbool"]), _ptr(m["pbits"]),
+                B, H, N, int(seqlen_orig), D, block_mask.Q_BLOCK_SIZE, block_mask.KV_BLOCK_SIZE,
+                int(m["idx"].shape[3]), m["num_partial"], 1 if q.dtype == torch.bfloat16 else 0,
+                float(scale) if scale is not None else 0.0, stream, _ptr(status))
+    _check(rc)
+
+
+def _pad_to_block(x: Tensor, block: int) -> Tuple[Tensor, int]:
+    n = x.shape[2]
+    rem = (-n) % block
+    if rem == 0:
+        return x, n
+    return torch.nn.functional.pad(x, (0, 0, 0, rem)), n
+
+
+def omni_attention(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMask,
+                   scale: Optional[float] = None, return_lse: bool = False, kernel: str = "ws",
+                   check_status: bool = False) -> Union[Tensor, Tuple[Tensor, Tensor]]:
+    """Block-mask attention forward on a B200.
+
+    query/key/value: [B, H, N, D] fp16 or bf16 CUDA tensors with Q_len == KV_len, D in {64, 128};
+    ``block_mask`` built for the length padded to 128. Returns ``out[:, :, :N]`` (and
+    ``lse[:, :, :N]``, natural log, when ``return_lse``). ``check_status=True`` synchronises and
+    raises if the kernel reported a bounded-wait timeout or an out-of-range block index.
+    """
+    B, H, Q, D = query.shape
+    if key.shape != (B, H, Q, D) or value.shape != (B, H, Q, D):
+        raise OmniAttnError(f"key/value shape must equal query shape {(B, H, Q, D)} (Q_len == KV_len)")
+    if D not in (64, 128):
+        raise ValueError(f"Unsupported head_dim={D}. Built for sm_100a: 64, 128.")
+    if block_mask.Q_BLOCK_SIZE != 128 or block_mask.KV_BLOCK_SIZE != 128:
+        raise ValueError("Unsupported block size: Q_BLOCK_SIZE and KV_BLOCK_SIZE must be 128.")
+    qp, n_orig = _pad_to_block(query, 128)
+    kp, _ = _pad_to_block(key, 128)
+    vp, _ = _pad_to_block(value, 128)
+    if qp.shape[2] != block_mask.q_len or kp.shape[2] != block_mask.kv_len:
+        raise OmniAttnError(
+            f"padded length {qp.shape[2]} does not match the mask's q_len/kv_len ({block_mask.q_len}/{block_mask.kv_len})")
+    qp, kp, vp = qp.contiguous(), kp.contiguous(), vp.contiguous()
+    out = torch.empty_like(qp)
+    lse = torch.empty(B, H, qp.shape[2], dtype=torch.float32, device=qp.device) if return_lse else None
+    status = torch.zeros(1, dtype=torch.int32, device=qp.device) if check_status else None
+    omni_attention_forward_out(qp, kp, vp, out, block_mask, n_orig, scale, lse, status, kernel)
+    if check_status:
+        code = int(status.item())
+        if code & 0xFF == STATUS_WAIT_TIMEOUT:
+            raise OmniAttnError(f"kernel gave up waiting (status {code:#x}); output is not valid")
+        if code & 0xFF == STATUS_BAD_INDEX:
+            raise OmniAttnError("kv_indices holds a block id outside [0, num_kv_blocks); the entry was skipped")
+    out = out[:, :, :n_orig]
+    if return_lse:
+        return out, lse[:, :, :n_orig]
+    return out
+
+
+def default_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)
