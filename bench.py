@@ -1,0 +1,349 @@
+#!/usr/bin/env python
+"""Benchmark of the omni-attention forward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload C4] [--no-c5]
+
+One "step" = one forward pass of the block-mask attention over one batch of synthetic input.
+Workload at every N: the 8K interleaved text/image configuration (C4: H32 N8192 D128 bf16, block
+128), one batch element per GPU (batch*heads are independent, so ranks share nothing and there
+is no collective on the data path: weak scaling). Metric: effective TFLOP/s counting only the
+4*128*128*D flops of visited blocks. Prints ONE JSON line on rank 0.
+
+Timing: W warm-up steps, then K steps each bracketed by CUDA events on the launching stream with a
+256 MiB L2 flush before every step (not timed); the per-rank sum is reduced with MAX over ranks.
+`e2e` is the same metric through the public Python operator with pinned HOST buffers, the
+host->device copies of q, k, v and the device->host copy of the output inside the timed region.
+`--impl reference` times the reference's CPU torch path (the oracle's restatement of
+omni_attn_torch.naive_attention_with_dense_mask) on this host's cores; one step = one head.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from omni_attention_b200 import inputs  # noqa: E402
+
+METRIC = "effective_tflops_nonempty_blocks"
+UNIT = "TFLOP/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the timed kernel on this
+# workload, from the ncu capture summarised in profiles/ (None until captured).
+NCU_DRAM_BYTES_PER_LAUNCH = {"C4": None}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d.get("hbm_gbs", 0.0)), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, device_index: int, period_s: float = 0.005):
+        super().__init__(daemon=True)
+        self.period = period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            try:
+                uuid = torch.cuda.get_device_properties(device_index).uuid
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake_slowdown",
+        }
+        while not self._halt.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    r = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                except Exception:
+                    r = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._halt.set()
+        self.join(timeout=1.0)
+        s = sorted(self.samples)
+        med = s[len(s) // 2] if s else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def device_qkv(B, H, N, D, dtype, seed, device, scale):
+    g = torch.Generator(device=device).manual_seed(seed)
+    mk = lambda: (torch.randn(B, H, N, D, generator=g, device=device, dtype=torch.float32) * scale).to(dtype)
+    return mk(), mk(), mk()
+
+
+def time_steps(fn, steps, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    evs = []
+    for _ in range(steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        evs.append((e0, e1))
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in evs)  # ms over all steps
+
+
+def cpu_baseline(cfg, bm, budget_s=15.0, max_heads=4):
+    """Reference torch path on this host's cores on a bounded sample of the same workload."""
+    from oracle import omni_oracle as orc
+
+    q, k, v = inputs.make_qkv(1, cfg.H, cfg.N, cfg.D, cfg.dtype, 0, cfg.qkv_scale, bh_range=(0, max_heads))
+    one = bm.slice_heads(0, max_heads)
+    per_head_blocks = [inputs.effective_flops(one.slice_heads(h, h + 1), cfg.D) for h in range(max_heads)]
+    t_total, fl, done = 0.0, 0, 0
+    for h in range(max_heads):
+        t0 = time.perf_counter()
+        orc.block_mask_attention(q, k, v, one, bh=[(0, h)])
+        t_total += time.perf_counter() - t0
+        fl += per_head_blocks[h]
+        done += 1
+        if t_total > budget_s:
+            break
+    return {"value": fl / t_total / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{done} of {cfg.H} heads of one {cfg.name} batch element, fp32 torch CPU, dense [N,N] scores per head",
+            "ms_per_head": 1e3 * t_total / done}
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the reference's CPU torch path (oracle restatement) on the host cores."""
+    if rank != 0:
+        return
+    from oracle import omni_oracle as orc
+
+    cfg = inputs.CONFIGS[args.workload]
+    torch.set_num_threads(os.cpu_count() or 1)
+    bm, _ = inputs.make_block_mask(cfg, 0, B=1)
+    n_heads = min(cfg.H, args.steps + args.warmup)
+    q, k, v = inputs.make_qkv(1, cfg.H, cfg.N, cfg.D, cfg.dtype, 0, cfg.qkv_scale, bh_range=(0, n_heads))
+    one = bm.slice_heads(0, n_heads)
+    t_total, fl = 0.0, 0
+    for i in range(args.warmup + args.steps):
+        h = i % n_heads
+        t0 = time.perf_counter()
+        orc.block_mask_attention(q, k, v, one, bh=[(0, h)])
+        dt = time.perf_counter() - t0
+        if i >= args.warmup:
+            t_total += dt
+            fl += inputs.effective_flops(one.slice_heads(h, h + 1), cfg.D)
+    val = fl / t_total / 1e12
+    cores = torch.get_num_threads()
+    sample = f"one step = one head ({cfg.N}x{cfg.N} fp32 scores) of the {cfg.name} workload; torch CPU, {cores} threads"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * t_total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{cfg.name}: B=n_gpus H={cfg.H} N={cfg.N} D={cfg.D} block 128 interleaved text/image mask",
+                   "step": "one head of one batch element on the host CPU"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+def run_ours(args, rank, local_rank, world):
+    import torch.distributed as dist
+
+    from omni_attention_b200.ops import omni_attention, omni_attention_forward_out
+
+    cfg = inputs.CONFIGS[args.workload]
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    # one batch element per rank; every rank draws its own image/text layout
+    bm, _ = inputs.make_block_mask(cfg, seed=rank, B=1)
+    flops = inputs.effective_flops(bm, cfg.D)
+    q, k, v = device_qkv(1, cfg.H, cfg.N, cfg.D, cfg.dtype, 1234 + rank, dev, cfg.qkv_scale)
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        omni_attention_forward_out(q, k, v, out, bm, cfg.N, None, None, status, "ws")
+
+    step()  # builds the cached device copy of the mask (+ bit-packed partial pool), not a timed step
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    total_ms = time_steps(step, args.steps, args.warmup, flush)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if int(status.item()) != 0:
+        raise RuntimeError(f"kernel status {int(status.item()):#x}")
+
+    # ---- end to end through the public operator with host buffers -------------------------------
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty_like(hq).pin_memory()
+    e2e_steps = max(3, min(args.steps, 20))
+
+    def e2e_step():
+        dq, dk, dv = (t.to(dev, non_blocking=True) for t in (hq, hk, hv))
+        o = omni_attention(dq, dk, dv, bm)
+        ho.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+
+    # ---- C5 (32K multi-image), batch*heads sharded over the ranks: strong scaling, reported aside --
+    c5 = None
+    if not args.no_c5:
+        c5cfg = inputs.CONFIGS["C5"]
+        bm5, _ = inputs.make_block_mask(c5cfg, seed=0)
+        BH = c5cfg.B * c5cfg.H
+        lo, hi = rank * BH // world, (rank + 1) * BH // world
+        shard = bm5.slice_heads(lo, hi)
+        fl5 = inputs.effective_flops(bm5, c5cfg.D)
+        q5, k5, v5 = device_qkv(1, hi - lo, c5cfg.N, c5cfg.D, c5cfg.dtype, 99 + rank, dev, c5cfg.qkv_scale)
+        o5 = torch.empty_like(q5)
+
+        def step5():
+            omni_attention_forward_out(q5, k5, v5, o5, shard, c5cfg.N, None, None, status, "ws")
+
+        step5()
+        if world > 1:
+            dist.barrier()
+        ms5 = time_steps(step5, 5, 3, flush) / 5
+        c5 = {"ms": ms5, "flops_all_ranks": fl5}
+        del q5, k5, v5, o5
+
+    # ---- reduce over ranks (MAX of time, SUM of work) ---------------------------------------------
+    vals = torch.tensor([total_ms, e2e_ms, c5["ms"] if c5 else 0.0, float(flops)], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = vals.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = vals.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, e2e_ms, c5ms, flops_all = float(mx[0]), float(mx[1]), float(mx[2]), float(sm[3])
+    else:
+        c5ms, flops_all = float(vals[2]), float(flops)
+    if rank != 0:
+        return
+
+    ms_per_step = total_ms / args.steps
+    value = flops_all / (ms_per_step * 1e-3) / 1e12
+    peak_tf, peak_hbm, which = measured_peaks()
+    per_gpu_tf = flops / (ms_per_step * 1e-3) / 1e12
+    e2e_val = flops_all / (e2e_ms / e2e_steps * 1e-3) / 1e12
+    tensor_bytes = q.numel() * q.element_size()
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"{cfg.name}: B=n_gpus({world}) H={cfg.H} N={cfg.N} D={cfg.D} bf16 block 128, interleaved text/image mask "
+                               f"(1024-token images), one batch element per GPU, batch*heads sharded, no collective",
+                   "visited_blocks_per_gpu": bm.visited_blocks(), "effective_gflop_per_gpu": flops / 1e9,
+                   "l2": "256 MiB flush before every timed step; q,k,v,o of a step total 268 MB (> 126 MB L2)",
+                   "kernel": "omni_fwd_ws_kernel<128,bf16>"},
+        "fwd_ms": ms_per_step,
+        "roofline": {"bound": "tensor", "achieved": per_gpu_tf, "peak": peak_tf, "unit": UNIT, "frac": per_gpu_tf / peak_tf,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(cfg.name), "peak_source": f"MEASURED_PEAKS.json bf16_tflops ({which}, burst)",
+                     "frac_of_nominal_2250": per_gpu_tf / 2250.0},
+        "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": 3 * tensor_bytes, "d2h_bytes_per_step": tensor_bytes,
+                "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+    }
+    if c5 is not None:
+        line["c5_sharded"] = {"workload": "C5: B=4 H=32 N=32768 D=128 bf16, 128 (batch,head) pairs split over the ranks (strong scaling)",
+                              "fwd_ms": c5ms, "value": c5["flops_all_ranks"] / (c5ms * 1e-3) / 1e12, "unit": UNIT, "steps": 5}
+    if world == 1 and not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)
+        line["cpu_baseline"] = cpu_baseline(cfg, bm)
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="C4", choices=["C3", "C4"])
+    ap.add_argument("--no-c5", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, local_rank, world)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

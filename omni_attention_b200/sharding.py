@@ -1,0 +1,79 @@
+"""Multi-GPU use: shard the flattened (batch * head) axis across ranks.
+
+Every (batch, head) pair is an independent attention problem with its own rows of the block lists
+(the reference's grid is (num_q_blocks, B*H), omni-attn-mma/mma/omni_attn_shared_kv.cu:789-790), so
+ranks never exchange anything on the data path. The only collective offered is an optional
+all-gather of the outputs for callers that want the full tensor on every rank.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from .block_mask import OmniBlockMask
+
+
+def shard_range(total_bh: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous range of (batch*head) pairs owned by ``rank``: sizes differ by at most one."""
+    base, rem = divmod(total_bh, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def balanced_shard_ranges(work_per_bh: Tensor, world: int) -> List[Tuple[int, int]]:
+    """Contiguous ranges whose summed work (e.g. visited blocks per pair) is as close to even as a greedy
+    prefix split gets (a pair joins the current rank while that brings the running total closer to the
+    rank's target); every rank gets at least one pair when there are enough pairs."""
+    n = int(work_per_bh.numel())
+    w = work_per_bh.double().flatten()
+    total = float(w.sum())
+    bounds, acc, start = [], 0.0, 0
+    for r in range(world):
+        if r == world - 1:
+            end = n
+        else:
+            target = total * (r + 1) / world
+            end = start
+            while end < n - (world - 1 - r) and (end == start or abs(acc + float(w[end]) - target) <= abs(acc - target)):
+                acc += float(w[end])
+                end += 1
+        bounds.append((start, end))
+        start = end
+    return bounds
+
+
+def shard_block_mask(bm: OmniBlockMask, rank: int, world: int) -> Tuple[OmniBlockMask, Tuple[int, int]]:
+    B, H, _ = bm.kv_num_blocks.shape
+    lo, hi = shard_range(B * H, rank, world)
+    return bm.slice_heads(lo, hi), (lo, hi)
+
+
+def shard_qkv(t: Tensor, rank: int, world: int) -> Tensor:
+    """[B, H, N, D] -> [1, n_local, N, D] view of this rank's pairs."""
+    B, H, N, D = t.shape
+    lo, hi = shard_range(B * H, rank, world)
+    return t.reshape(B * H, N, D)[lo:hi].unsqueeze(0)
+
+
+def all_gather_outputs(local_out: Tensor, total_bh: int, group=None) -> Tensor:
+    """Optional epilogue: gather every rank's [1, n_local, N, D] output into [total_bh, N, D] on all
+    ranks (NCCL on GPUs, gloo on CPU). Not part of the timed forward."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    N, D = local_out.shape[2:]
+    sizes = [shard_range(total_bh, r, world) for r in range(world)]
+    parts = [torch.empty(hi - lo, N, D, dtype=local_out.dtype, device=local_out.device) for lo, hi in sizes]
+    dist.all_gather(parts, local_out.reshape(-1, N, D).contiguous(), group=group)
+    return torch.cat(parts, 0)
+
+
+def max_over_ranks(value: float, device: Optional[torch.device] = None, group=None) -> float:
+    """A time reported for a multi-GPU step is the slowest rank's."""
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t[0])

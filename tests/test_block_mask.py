@@ -1,0 +1,140 @@
+"""Host-side mask builders of the package against the oracle's restatements of the reference."""
+import os
+import sys
+
+import pytest
+import torch
+
+from conftest import GOLDEN_CASES, load_golden
+from omni_attention_b200 import inputs
+from omni_attention_b200.block_mask import (BlockMaskType, OmniBlockMask, block_mask_from_dense,
+                                            block_mask_from_row_limits, build_partial_block_data,
+                                            create_causal_omni_block_mask, dense_mask_from_blocks,
+                                            row_limits_from_modality_positions)
+from oracle import omni_oracle as orc
+
+REF_DIR = os.environ.get("OMNI_REFERENCE_DIR", "/root/reference/omni-attn-mma")
+
+
+def test_type_codes_match_reference_enum():
+    assert (int(BlockMaskType.MASKED), int(BlockMaskType.CAUSAL), int(BlockMaskType.FULL), int(BlockMaskType.PARTIAL)) == (0, 1, 2, 3)
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_vectorised_expansion_matches_golden_dense_mask(name):
+    g = load_golden(name)
+    assert torch.equal(dense_mask_from_blocks(g["bm"]), g["dense"])
+    assert torch.equal(g["bm"].to_dense_mask(), g["dense"])
+    B, H = g["dense"].shape[:2]
+    part = dense_mask_from_blocks(g["bm"], (B * H - 1, B * H))
+    assert torch.equal(part[0], g["dense"][B - 1, H - 1])
+
+
+@pytest.mark.parametrize("name", ["ref_fcp_n512_d64", "ref_interleaved_n512_d64"])
+def test_build_partial_block_data_matches_reference_layout(name):
+    g = load_golden(name)
+    bm = g["bm"]
+    idx, pool = build_partial_block_data(bm, g["dense"])
+    assert torch.equal(idx, bm.partial_block_mask_indices)
+    assert torch.equal(pool, bm.partial_block_masks)
+
+
+def test_partial_without_pool_falls_back_to_causal():
+    g = load_golden("ref_fcp_n512_d64")
+    bm = g["bm"]
+    stripped = OmniBlockMask(bm.kv_num_blocks, bm.kv_indices, bm.block_mask_types, bm.q_len, bm.kv_len)
+    assert torch.equal(dense_mask_from_blocks(stripped), orc.to_dense_mask_loops(stripped))
+
+
+def test_causal_builder():
+    bm = create_causal_omni_block_mask(2, 3, 500, 500)
+    assert bm.q_len == 512 and bm.kv_num_blocks.shape == (2, 3, 4)
+    dense = bm.to_dense_mask()
+    want = torch.tril(torch.ones(512, 512, dtype=torch.bool))
+    assert torch.equal(dense[1, 2], want)
+    assert bm.kv_num_blocks[0, 0].tolist() == [1, 2, 3, 4]
+    assert bm.visited_blocks() == 2 * 3 * 10
+
+
+@pytest.mark.parametrize("share", [True, False])
+def test_row_limit_builder_matches_dense_derivation(share):
+    N, H = 1024, 2
+    spans = [[(100, 256), (600, 130)], [(0, 128), (128, 128), (700, 300)]]
+    limits, causal_rows = row_limits_from_modality_positions(N, spans)
+    bm = block_mask_from_row_limits(limits, H, causal_rows, 128, share_partial_across_heads=share)
+    mods = [torch.tensor([[1, o, l] for o, l in s] + [[1, 0, 0]] * (3 - len(s))) for s in spans]
+    dense = orc.naive_attn_mask(N, torch.stack(mods))  # [B, N, N]
+    got = bm.to_dense_mask()
+    for b in range(2):
+        for h in range(H):
+            assert torch.equal(got[b, h], dense[b])
+        bounds = [x for o, l in spans[b] for x in (o, o + l)]
+        want_types = orc.block_types_from_dense(dense[b], 128, bounds)
+        grid = torch.zeros(8, 8, dtype=torch.int32)
+        for qb in range(8):
+            n = int(bm.kv_num_blocks[b, 0, qb])
+            ids = bm.kv_indices[b, 0, qb, :n].long()
+            assert ids.tolist() == sorted(ids.tolist())
+            grid[qb, ids] = bm.block_mask_types[b, 0, qb, :n]
+        assert torch.equal(grid, want_types)
+    if not share:
+        idx, pool = build_partial_block_data(bm, got)
+        assert torch.equal(idx, bm.partial_block_mask_indices)
+        assert torch.equal(pool, bm.partial_block_masks)
+
+
+def test_block_mask_from_dense_round_trip():
+    torch.manual_seed(0)
+    dense = torch.rand(1, 2, 384, 384) < 0.5
+    dense[:, :, :128, 128:] = False
+    dense[:, :, 128:256, :128] = True
+    dense[0, 0, :128, :128] = torch.tril(torch.ones(128, 128, dtype=torch.bool))
+    bm = block_mask_from_dense(dense)
+    assert torch.equal(bm.to_dense_mask(), dense)
+    assert int(bm.block_mask_types[0, 0, 0, 0]) == BlockMaskType.CAUSAL
+    assert int(bm.kv_num_blocks[0, 0, 0]) == 1
+
+
+@pytest.mark.parametrize("name", ["C1", "C2", "C3"])
+def test_config_generators(name):
+    cfg = inputs.CONFIGS[name]
+    bm, meta = inputs.make_block_mask(cfg, seed=0)
+    bm2, _ = inputs.make_block_mask(cfg, seed=0)
+    assert torch.equal(bm.kv_indices, bm2.kv_indices) and torch.equal(bm.block_mask_types, bm2.block_mask_types)
+    assert bm.kv_num_blocks.shape == (cfg.B, cfg.H, cfg.N // 128)
+    dense = dense_mask_from_blocks(bm, (0, 1))[0]
+    assert bool(dense.any(-1).all()), "every query row must keep at least one key"
+    assert torch.equal(dense, orc.to_dense_mask_slice(bm, 0, 0))
+    assert not bool(torch.triu(dense, 1).any()) or name == "C3"
+    if name == "C3":
+        spans = meta["image_spans"][0]
+        mods = torch.tensor([[[1, o, l] for o, l in spans]])
+        assert torch.equal(dense, orc.naive_attn_mask(cfg.N, mods)[0])
+    assert inputs.effective_flops(bm, cfg.D) == 4 * 128 * 128 * cfg.D * bm.visited_blocks()
+
+
+def test_qkv_sharding_is_consistent():
+    q, k, v = inputs.make_qkv(1, 4, 256, 64, torch.bfloat16, seed=3, qkv_scale=0.5)
+    qs, ks, vs = inputs.make_qkv(1, 4, 256, 64, torch.bfloat16, seed=3, qkv_scale=0.5, bh_range=(2, 4))
+    assert torch.equal(qs[0], q[0, 2:4]) and torch.equal(vs[0], v[0, 2:4])
+    bm = create_causal_omni_block_mask(2, 2, 256, 256)
+    sl = bm.slice_heads(1, 3)
+    assert sl.kv_num_blocks.shape == (1, 2, 2)
+    assert torch.equal(sl.kv_indices[0, 0], bm.kv_indices[0, 1])
+    assert torch.equal(sl.kv_indices[0, 1], bm.kv_indices[1, 0])
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_DIR), reason="reference checkout not present")
+def test_builders_against_reference_in_process():
+    sys.path.insert(0, REF_DIR)
+    import omni_attn_torch as ref  # reference module
+
+    r = ref.create_causal_omni_block_mask(1, 2, 300, 300, 128, 128, device="cpu")
+    m = create_causal_omni_block_mask(1, 2, 300, 300)
+    for f in ("kv_num_blocks", "kv_indices", "block_mask_types"):
+        assert torch.equal(getattr(r, f), getattr(m, f))
+    assert (r.q_len, r.kv_len) == (m.q_len, m.kv_len)
+    g = load_golden("ref_interleaved_n512_d64")
+    idx, pool = ref.build_partial_block_data(g["bm"], g["dense"])
+    mi, mp = build_partial_block_data(g["bm"], g["dense"])
+    assert torch.equal(idx, mi) and torch.equal(pool, mp)

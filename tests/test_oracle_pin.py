@@ -1,0 +1,112 @@
+"""Pins the CPU oracle: against the golden vectors produced by running the reference
+(tests/golden/make_golden.py) and, where the reference checkout is present, against the reference's
+own functions called in-process on fresh seeded inputs."""
+import math
+import os
+import sys
+
+import pytest
+import torch
+
+from conftest import GOLDEN_CASES, load_golden
+from oracle import omni_oracle as orc
+from oracle import scalar
+
+REF_DIR = os.environ.get("OMNI_REFERENCE_DIR", "/root/reference/omni-attn-mma")
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_dense_mask_matches_reference_expansion(name):
+    g = load_golden(name)
+    bm = g["bm"]
+    assert torch.equal(orc.to_dense_mask_loops(bm), g["dense"])
+    B, H = g["dense"].shape[:2]
+    for b in range(B):
+        for h in range(H):
+            assert torch.equal(orc.to_dense_mask_slice(bm, b, h), g["dense"][b, h])
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_attention_matches_reference_output(name):
+    g = load_golden(name)
+    out, lse = orc.block_mask_attention(g["q"], g["k"], g["v"], g["bm"])
+    # same torch ops on the same values: bit-exact on the same build, allow rounding noise across builds
+    assert torch.allclose(out, g["out"], atol=2e-6, rtol=1e-6)
+    assert torch.allclose(lse, g["lse"], atol=2e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_scalar_oracle_matches_reference_output(name):
+    g = load_golden(name)
+    B, H, N, D = g["q"].shape
+    rows_bh = [bh for bh in range(B * H) for _ in range(N)]
+    rows_q = list(range(N)) * (B * H)
+    out, lse = scalar.oracle_rows(g["q"], g["k"], g["v"], g["bm"], rows_bh, rows_q)
+    assert torch.allclose(out.view(B, H, N, D), g["out"], atol=5e-6, rtol=1e-5)
+    assert torch.allclose(lse.view(B, H, N), g["lse"], atol=5e-6, rtol=1e-5)
+
+
+def test_scalar_oracle_clips_keys_and_zeroes_empty_rows():
+    g = load_golden("ref_causal_n256_d64")
+    B, H, N, D = g["q"].shape
+    bm = g["bm"]
+    seqlen_orig = 200
+    out, lse = scalar.oracle_rows(g["q"], g["k"], g["v"], bm, [0] * N, list(range(N)), seqlen_orig=seqlen_orig)
+    ro, rl = orc.block_mask_attention(g["q"], g["k"], g["v"], bm, bh=[(0, 0)], seqlen_orig=seqlen_orig)
+    assert torch.allclose(out[:seqlen_orig], ro[0, 0, :seqlen_orig], atol=5e-6)
+    assert torch.all(out[seqlen_orig:] == 0) and torch.all(torch.isinf(lse[seqlen_orig:]))
+    # a Q block with an empty list attends nothing: zeros, lse = -inf
+    bm2 = load_golden("ref_causal_n256_d64")["bm"]
+    bm2.kv_num_blocks[:, :, 1] = 0
+    out, lse = scalar.oracle_rows(g["q"], g["k"], g["v"], bm2, [0, 0], [5, 130])
+    assert torch.all(out[1] == 0) and math.isinf(float(lse[1])) and float(lse[1]) < 0
+    assert torch.any(out[0] != 0)
+
+
+def test_naive_attn_mask_rule():
+    mods = torch.tensor([[[1, 3, 4], [1, 10, 2]]])
+    m = orc.naive_attn_mask(16, mods)[0]
+    for i in range(16):
+        for j in range(16):
+            want = j <= i or (i >= 3 and j < 7) or (i >= 10 and j < 12)
+            assert bool(m[i, j]) == want
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_DIR), reason="reference checkout not present")
+def test_oracle_against_reference_in_process():
+    sys.path.insert(0, REF_DIR)
+    import naive_attn as ref_naive  # reference module
+    import omni_attn_torch as ref  # reference module
+
+    torch.manual_seed(123)
+    B, H, N, D = 1, 2, 384, 64
+    q, k, v = (torch.randn(B, H, N, D).half().float() for _ in range(3))
+    # random F/C/P/skip lists, PARTIAL blocks with Bernoulli masks, built with the reference's types
+    nq = N // 128
+    nb = torch.zeros(B, H, nq, dtype=torch.int32)
+    idx = torch.zeros(B, H, nq, nq, dtype=torch.int32)
+    typ = torch.zeros(B, H, nq, nq, dtype=torch.int32)
+    for h in range(H):
+        for qb in range(nq):
+            n = 0
+            for kb in range(qb + 1):
+                t = int(ref.BlockMaskType.CAUSAL) if kb == qb else int(torch.randint(0, 4, (1,)))
+                if t == 0:
+                    continue
+                idx[0, h, qb, n], typ[0, h, qb, n] = kb, t
+                n += 1
+            nb[0, h, qb] = n
+    rbm = ref.OmniBlockMask(nb, idx, typ, N, N, 128, 128)
+    dense_src = torch.rand(B, H, N, N) < 0.5
+    rbm.partial_block_mask_indices, rbm.partial_block_masks = ref.build_partial_block_data(rbm, dense_src)
+    dense = rbm.to_dense_mask()
+    assert torch.equal(orc.to_dense_mask_loops(rbm), dense)
+    ref_out = ref.naive_attention_with_dense_mask(q, k, v, mask=ref.to_score_mask(rbm))
+    ref_out2 = ref_naive.naive_attention(q, k, v, dense)
+    out, _ = orc.block_mask_attention(q, k, v, rbm)
+    assert torch.allclose(out, ref_out, atol=1e-6, rtol=1e-6)
+    assert torch.allclose(out, ref_out2, atol=1e-6, rtol=1e-6)
+    # dtype behaviour of the torch path with 16-bit inputs (softmax in fp32, cast back)
+    o16, _ = orc.attention_dense_mask(q.bfloat16(), k.bfloat16(), v.bfloat16(), ref.to_score_mask(rbm))
+    r16 = ref.naive_attention_with_dense_mask(q.bfloat16(), k.bfloat16(), v.bfloat16(), mask=ref.to_score_mask(rbm))
+    assert torch.equal(o16, r16)

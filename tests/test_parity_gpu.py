@@ -1,0 +1,278 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI (ctypes) and the pybind module.
+
+Tolerances (written once in conftest.py): output atol 2e-2 / rtol 1e-2, log-sum-exp 1e-3.
+"""
+import math
+
+import pytest
+import torch
+
+from conftest import GOLDEN_CASES, LSE_ATOL, assert_parity, load_golden
+from omni_attention_b200 import inputs, ops
+from omni_attention_b200.block_mask import (BlockMaskType, OmniBlockMask, create_causal_omni_block_mask,
+                                            dense_mask_from_blocks)
+from omni_attention_b200.ops import omni_attention
+from oracle import omni_oracle as orc
+from oracle import scalar
+
+pytestmark = pytest.mark.gpu
+KERNELS = ["ws", "simple"]
+
+
+def run(q, k, v, bm, dev, kernel="ws", **kw):
+    out, lse = omni_attention(q.to(dev), k.to(dev), v.to(dev), bm, return_lse=True, kernel=kernel, check_status=True, **kw)
+    return out, lse
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_golden_vectors_from_the_reference(cuda_device, name, kernel):
+    g = load_golden(name)
+    out, lse = run(g["q"], g["k"], g["v"], g["bm"], cuda_device, kernel)
+    assert_parity(out, lse, g["out"], g["lse"], f"{name}/{kernel}")
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_golden_vectors_bf16(cuda_device, name, kernel):
+    g = load_golden(name)
+    q, k, v = (g[x].bfloat16() for x in "qkv")
+    ref_out, ref_lse = orc.block_mask_attention(q, k, v, g["bm"])
+    out, lse = run(q, k, v, g["bm"], cuda_device, kernel)
+    assert out.dtype == torch.bfloat16
+    assert_parity(out, lse, ref_out, ref_lse, f"{name}/{kernel}/bf16")
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("cname", ["C1", "C2", "C3"])
+@pytest.mark.parametrize("seed", [0, 1])
+def test_benchmark_configs_full(cuda_device, cname, seed, kernel):
+    if kernel == "simple" and seed == 1:
+        pytest.skip("second seed only on the fast kernel")
+    q, k, v, bm, _ = inputs.make_inputs(cname, seed=seed)
+    ref_out, ref_lse = orc.block_mask_attention(q, k, v, bm)
+    out, lse = run(q, k, v, bm, cuda_device, kernel)
+    assert_parity(out, lse, ref_out, ref_lse, f"{cname}/seed{seed}/{kernel}")
+
+
+def _sample_rows(B, H, N, n, gen):
+    bh = torch.randint(0, B * H, (n,), generator=gen)
+    qi = torch.randint(0, N, (n,), generator=gen)
+    return bh.tolist(), qi.tolist()
+
+
+def test_config_c4_sampled_heads_and_rows(cuda_device):
+    q, k, v, bm, _ = inputs.make_inputs("C4", seed=0)
+    out, lse = run(q, k, v, bm, cuda_device)
+    out_s, lse_s = run(q, k, v, bm, cuda_device, "simple")
+    # two whole heads against the torch oracle
+    heads = [(0, 3), (0, 31)]
+    ref_out, ref_lse = orc.block_mask_attention(q, k, v, bm, bh=heads)
+    for b, h in heads:
+        assert_parity(out[b, h], lse[b, h], ref_out[b, h], ref_lse[b, h], f"C4 head {h}")
+        assert_parity(out_s[b, h], lse_s[b, h], ref_out[b, h], ref_lse[b, h], f"C4 head {h} simple")
+    # random rows of every head against the scalar oracle
+    g = torch.Generator().manual_seed(5)
+    rb, rq = _sample_rows(1, 32, 8192, 256, g)
+    so, sl = scalar.oracle_rows(q, k, v, bm, rb, rq)
+    got = out.float().cpu().view(32, 8192, 128)[rb, rq]
+    got_l = lse.cpu().view(32, 8192)[rb, rq]
+    assert_parity(got, got_l, so, sl, "C4 sampled rows")
+    # the two kernels agree with each other everywhere
+    assert_parity(out, lse, out_s.float(), lse_s, "C4 ws vs simple")
+
+
+def test_config_c5_shape_sharded_slice(cuda_device):
+    """The 32K multi-image configuration, the shard one of 8 GPUs would own (16 of the 128
+    batch*head pairs), checked on sampled rows and through properties that need no oracle."""
+    cfg = inputs.CONFIGS["C5"]
+    lo, hi = 48, 64  # batch element 1, heads 16..31
+    q, k, v, bm, _ = inputs.make_inputs("C5", seed=0, bh_range=(lo, hi))
+    out, lse = run(q, k, v, bm, cuda_device)
+    assert out.shape == (1, hi - lo, cfg.N, cfg.D)
+    assert not bool(torch.isnan(out).any()) and not bool(torch.isinf(lse).any())
+    g = torch.Generator().manual_seed(9)
+    rb, rq = _sample_rows(1, hi - lo, cfg.N, 96, g)
+    rq[:8] = [0, 127, 128, cfg.N - 1, cfg.N - 128, 4095, 4096, 20000]
+    so, sl = scalar.oracle_rows(q, k, v, bm, rb, rq)
+    got = out.float().cpu().view(hi - lo, cfg.N, cfg.D)[rb, rq]
+    got_l = lse.cpu().view(hi - lo, cfg.N)[rb, rq]
+    assert_parity(got, got_l, so, sl, "C5 sampled rows")
+    # linearity in V: out(V1 + V2) = out(V1) + out(V2); same attention weights, fp32 accumulation
+    v2 = torch.roll(v, 1, dims=2)
+    o_b, _ = run(q, k, v2, bm, cuda_device)
+    o_sum, lse2 = run(q, k, (v.float() + v2.float()).to(v.dtype), bm, cuda_device)
+    assert torch.equal(lse2, lse), "lse must not depend on V"
+    diff = (o_sum.float() - (out.float() + o_b.float())).abs().max().item()
+    assert diff <= 3e-2, diff
+    # a constant V column comes back unchanged: the attention weights of every row sum to one
+    vc = torch.full_like(v, 0.75)
+    o_c, _ = run(q, k, vc, bm, cuda_device)
+    assert (o_c.float() - 0.75).abs().max().item() <= 4e-3
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_edge_empty_lists_and_masked_entries(cuda_device, kernel):
+    g = load_golden("ref_fcp_n512_d64")
+    bm = g["bm"]
+    bm2 = OmniBlockMask(bm.kv_num_blocks.clone(), bm.kv_indices.clone(), bm.block_mask_types.clone(), bm.q_len,
+                        bm.kv_len, 128, 128, bm.partial_block_mask_indices.clone(), bm.partial_block_masks.clone())
+    bm2.kv_num_blocks[:, 0, 1] = 0                       # Q block 1 of head 0 attends nothing
+    bm2.block_mask_types[:, 1, 3, 1] = int(BlockMaskType.MASKED)   # a listed entry typed MASKED is skipped
+    bm2.kv_indices[:, 1, 2, 0] = 3                       # CAUSAL-typed? force an above-diagonal block id on a listed entry
+    bm2.block_mask_types[:, 1, 2, 0] = int(BlockMaskType.CAUSAL)  # CAUSAL above the diagonal contributes nothing
+    dense = dense_mask_from_blocks(bm2)
+    assert torch.equal(dense, orc.to_dense_mask_loops(bm2))
+    rows_ok = dense.any(-1)
+    out, lse = run(g["q"], g["k"], g["v"], bm2, cuda_device, kernel)
+    ref_out, ref_lse = orc.block_mask_attention(g["q"], g["k"], g["v"], bm2)
+    out, lse = out.float().cpu(), lse.cpu()
+    assert_parity(out[rows_ok], lse[rows_ok], ref_out[rows_ok], ref_lse[rows_ok], "rows with keys")
+    # rows that attend nothing: zeros and lse = -inf (the torch path gives NaN there, the
+    # reference's CUDA kernels give zeros: omni-attn-mma/mma/attn_naive.cu:178-183)
+    assert bool((~rows_ok).any())
+    assert torch.all(out[~rows_ok] == 0)
+    assert torch.all(torch.isinf(lse[~rows_ok]) & (lse[~rows_ok] < 0))
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_edge_ragged_length_padding_and_clipping(cuda_device, kernel):
+    """Unpadded length 300: the operator pads to 384; keys >= 300 are never attended even though the
+    block lists cover them, padded query rows are sliced off."""
+    torch.manual_seed(3)
+    n = 300
+    q, k, v = (torch.randn(1, 2, n, 128).half() for _ in range(3))
+    bm = create_causal_omni_block_mask(1, 2, n, n)
+    bm.block_mask_types[:, 1, 2, :] = int(BlockMaskType.FULL)   # head 1: last Q block sees every block fully
+    out, lse = run(q, k, v, bm, cuda_device, kernel)
+    assert out.shape == (1, 2, n, 128)
+    pad = lambda t: torch.nn.functional.pad(t, (0, 0, 0, 384 - n))
+    ref_out, ref_lse = orc.block_mask_attention(pad(q), pad(k), pad(v), bm, seqlen_orig=n)
+    assert_parity(out, lse, ref_out[:, :, :n], ref_lse[:, :, :n], "ragged")
+    so, sl = scalar.oracle_rows(pad(q), pad(k), pad(v), bm, [1, 1, 0], [299, 256, 299], seqlen_orig=n)
+    assert_parity(out.float().cpu()[0, [1, 1, 0], [299, 256, 299]], lse.cpu()[0, [1, 1, 0], [299, 256, 299]], so, sl, "ragged rows")
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_edge_partial_rows_without_keys_and_unsorted_lists(cuda_device, kernel):
+    torch.manual_seed(4)
+    N = 384
+    q, k, v = (torch.randn(1, 1, N, 64).bfloat16() for _ in range(3))
+    nb = torch.tensor([[[1, 2, 3]]], dtype=torch.int32)
+    idx = torch.tensor([[[[0, 0, 0], [1, 0, 0], [2, 0, 1]]]], dtype=torch.int32)          # last list unsorted
+    P, F, C = int(BlockMaskType.PARTIAL), int(BlockMaskType.FULL), int(BlockMaskType.CAUSAL)
+    typ = torch.tensor([[[[P, 0, 0], [C, P, 0], [P, F, P]]]], dtype=torch.int32)
+    pidx = torch.tensor([[[[0, -1, -1], [-1, 1, -1], [2, -1, 7]]]], dtype=torch.int32)     # 7 is out of range -> causal fallback
+    pool = torch.rand(3, 128, 128) < 0.3
+    pool[0, 5] = False          # a row of the only tile of Q block 0 with no allowed key at all
+    pool[0, 0, 0] = True
+    bm = OmniBlockMask(nb, idx, typ, N, N, 128, 128, pidx, pool)
+    dense = dense_mask_from_blocks(bm)
+    assert torch.equal(dense, orc.to_dense_mask_loops(bm))
+    rows_ok = dense.any(-1)
+    assert not bool(rows_ok[0, 0, 5])
+    out, lse = run(q, k, v, bm, cuda_device, kernel)
+    ref_out, ref_lse = orc.block_mask_attention(q, k, v, bm)
+    out, lse = out.float().cpu(), lse.cpu()
+    assert_parity(out[rows_ok], lse[rows_ok], ref_out[rows_ok], ref_lse[rows_ok], "partial")
+    assert torch.all(out[~rows_ok] == 0) and torch.all(lse[~rows_ok] == -math.inf)
+    # byte-per-element pool (the reference's format) and the bit-packed pool give identical results
+    ob, lb = omni_attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), bm, return_lse=True, kernel=kernel)
+    bm_bytes = OmniBlockMask(nb, idx, typ, N, N, 128, 128, pidx, pool)
+    o2 = torch.empty_like(ob)
+    l2 = torch.empty_like(lb)
+    ops.omni_attention_forward_out(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), o2, bm_bytes, N, None, l2, None,
+                                   kernel, pack_bits=False)
+    assert torch.equal(o2, ob) and torch.equal(l2, lb)
+
+
+def test_pack_partial_masks_bit_layout(cuda_device):
+    pool = torch.rand(5, 128, 128) < 0.5
+    bits = ops.pack_partial_masks(pool.to(cuda_device)).cpu()
+    w = bits.view(5, 128, 4).to(torch.int64) & 0xFFFFFFFF
+    unpacked = ((w.unsqueeze(-1) >> torch.arange(32)) & 1).bool().view(5, 128, 128)
+    assert torch.equal(unpacked, pool)
+
+
+def test_bad_block_index_is_reported_not_dereferenced(cuda_device):
+    g = load_golden("ref_causal_n256_d64")
+    bm = g["bm"]
+    bad = OmniBlockMask(bm.kv_num_blocks.clone(), bm.kv_indices.clone(), bm.block_mask_types.clone(), 256, 256)
+    bad.kv_indices[0, 0, 1, 0] = 99
+    with pytest.raises(ops.OmniAttnError, match="block id"):
+        omni_attention(g["q"].to(cuda_device), g["k"].to(cuda_device), g["v"].to(cuda_device), bad, check_status=True)
+
+
+def test_scale_argument_is_honoured(cuda_device):
+    g = load_golden("ref_causal_n256_d64")
+    s = 0.05
+    ref_out, ref_lse = orc.block_mask_attention(g["q"], g["k"], g["v"], g["bm"], scale=s)
+    out, lse = run(g["q"], g["k"], g["v"], g["bm"], cuda_device, "ws", scale=s)
+    assert_parity(out, lse, ref_out, ref_lse, "scale")
+
+
+def test_runs_on_a_side_stream_without_device_sync(cuda_device):
+    g = load_golden("ref_fcp_n384_d128")
+    q, k, v = (g[x].to(cuda_device) for x in "qkv")
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        out = omni_attention(q, k, v, g["bm"])
+    st.synchronize()
+    assert_parity(out, None, g["out"], None, "side stream")
+
+
+def test_reference_pybind_surface(cuda_device):
+    """The reference's 13-argument entry points, called exactly as its wrapper does
+    (omni-attn-mma/omni_attn_torch.py:652-663): caller-allocated O, int32 mask tensors, bool pool."""
+    import omni_attention_b200 as pkg
+
+    m = pkg.install_reference_module()
+    g = load_golden("ref_interleaved_n512_d64")
+    bm = g["bm"]
+    dev = cuda_device
+    q, k, v = (g[x].to(dev).contiguous() for x in "qkv")
+    args = lambda o: (q, k, v, o, bm.kv_num_blocks.to(dev).int().contiguous(), bm.kv_indices.to(dev).int().contiguous(),
+                      bm.block_mask_types.to(dev).int().contiguous(), 128, 128, 512,
+                      bm.partial_block_mask_indices.to(dev).int().contiguous(), bm.partial_block_masks.to(dev).contiguous(), True)
+    for name in ("omni_attn_mma_stages_split_q_shared_kv", "omni_attn_simple_kernel", "omni_attn_cp_async",
+                 "omni_attn_preftech_kernel", "omni_attn_mma_stages_split_q_shared_kv_swizzle"):
+        o = torch.empty_like(q)
+        assert getattr(m, name)(*args(o)) is None
+        torch.cuda.synchronize()
+        assert_parity(o, None, g["out"], None, name)
+    # has_partial = False with empty placeholders, causal mask
+    gc = load_golden("ref_causal_n256_d64")
+    q, k, v = (gc[x].to(dev).contiguous() for x in "qkv")
+    o = torch.empty_like(q)
+    c = gc["bm"]
+    m.omni_attn_mma_stages_split_q_shared_kv(q, k, v, o, c.kv_num_blocks.to(dev), c.kv_indices.to(dev), c.block_mask_types.to(dev),
+                                             128, 128, 256, torch.empty(0, dtype=torch.int32, device=dev),
+                                             torch.empty(0, dtype=torch.bool, device=dev), False)
+    torch.cuda.synchronize()
+    assert_parity(o, None, gc["out"], None, "no partial")
+    # the reference launchers' errors
+    with pytest.raises(RuntimeError):
+        m.omni_attn_simple_kernel(q.float(), k.float(), v.float(), o.float(), c.kv_num_blocks.to(dev), c.kv_indices.to(dev),
+                                  c.block_mask_types.to(dev), 128, 128, 256, torch.empty(0, dtype=torch.int32, device=dev),
+                                  torch.empty(0, dtype=torch.bool, device=dev), False)
+    with pytest.raises(RuntimeError, match="Q blocks"):
+        m.omni_attn_simple_kernel(q, k, v, o, c.kv_num_blocks.to(dev)[:, :, :1].contiguous(), c.kv_indices.to(dev),
+                                  c.block_mask_types.to(dev), 128, 128, 256, torch.empty(0, dtype=torch.int32, device=dev),
+                                  torch.empty(0, dtype=torch.bool, device=dev), False)
+    with pytest.raises(RuntimeError, match="block size"):
+        m.omni_attn_simple_kernel(q, k, v, o, c.kv_num_blocks.to(dev), c.kv_indices.to(dev), c.block_mask_types.to(dev), 128, 64,
+                                  256, torch.empty(0, dtype=torch.int32, device=dev), torch.empty(0, dtype=torch.bool, device=dev), False)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        m.omni_attn_simple_kernel(q.transpose(1, 2).contiguous().transpose(1, 2), k, v, o, c.kv_num_blocks.to(dev), c.kv_indices.to(dev),
+                                  c.block_mask_types.to(dev), 128, 128, 256, torch.empty(0, dtype=torch.int32, device=dev),
+                                  torch.empty(0, dtype=torch.bool, device=dev), False)
+    # superset entry: scale, lse, status
+    lse = torch.empty(1, 2, 256, dtype=torch.float32, device=dev)
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    m.omni_attn_fwd(q, k, v, o, c.kv_num_blocks.to(dev), c.kv_indices.to(dev), c.block_mask_types.to(dev), 128, 128, 256,
+                    torch.empty(0, dtype=torch.int32, device=dev), torch.empty(0, dtype=torch.bool, device=dev), False,
+                    scale=None, lse=lse, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert float((lse.cpu() - gc["lse"]).abs().max()) <= LSE_ATOL
