@@ -3,6 +3,7 @@
 // exceptions), TMA tensor-map construction and kernel dispatch.
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 
 #include "../../include/omni_attn_sm100.h"
 #include "omni_launch.h"
@@ -11,6 +12,7 @@ namespace omni {
 namespace {
 
 thread_local int g_last_cuda_error = 0;
+long long* g_prof_buffer = nullptr;  // set only through the OMNI_PROFILE debug entry point
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -51,6 +53,23 @@ int make_tile_map(CUtensorMap* tm, const void* base, long long rows, int head_di
     return OMNI_ERR_CUDA;
   }
   return OMNI_OK;
+}
+
+// Heads per scheduling group of the warp-specialised kernel: as many heads as keep the group's K and
+// V (2 * N * D * 2 bytes per head) inside an L2 budget, 48 MB of the B200's 126 MB unless the
+// environment variable OMNI_ATTN_L2_MB says otherwise.
+int group_heads_for(long long BH, int seqlen, int head_dim) {
+  static long long budget = -1;
+  if (budget < 0) {
+    const char* e = std::getenv("OMNI_ATTN_L2_MB");
+    const long long mb = e != nullptr ? std::atoll(e) : 48;
+    budget = (mb > 0 ? mb : 48) << 20;
+  }
+  const long long per_head = 4LL * seqlen * head_dim;
+  long long g = budget / per_head;
+  if (g < 1) g = 1;
+  if (g > BH) g = BH;
+  return static_cast<int>(g);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -103,6 +122,7 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
   p.partial_bits = num_partial > 0 ? partial_bits : nullptr;
   p.status = status;
   p.work_order = nullptr;
+  p.prof = g_prof_buffer;
   p.BH = static_cast<int>(BH);
   p.N = seqlen_padded;
   p.seqlen_orig = seqlen_orig;
@@ -111,6 +131,8 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
   p.num_partial = num_partial;
   p.scale = scale > 0.f ? scale : 1.f / std::sqrt(static_cast<float>(head_dim));
   p.scale_log2 = p.scale * 1.4426950408889634f;
+  p.inv_scale_log2 = 1.f / p.scale_log2;
+  p.group_heads = group_heads_for(BH, seqlen_padded, head_dim);
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = simple ? launch_simple(head_dim, bf16, tmQ, tmK, tmV, p, st)
@@ -208,5 +230,9 @@ const char* omni_attn_error_string(int code) {
 int omni_attn_last_cuda_error(void) { return omni::g_last_cuda_error; }
 
 int omni_attn_abi_version(void) { return OMNI_ATTN_ABI_VERSION; }
+
+#ifdef OMNI_PROFILE
+void omni_attn_debug_set_prof(long long* device_buffer) { omni::g_prof_buffer = device_buffer; }
+#endif
 
 }  // extern "C"

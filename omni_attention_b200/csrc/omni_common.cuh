@@ -41,14 +41,17 @@ struct FwdParams {
   const uint32_t* partial_bits;   // [P, 128, 4] words (bit c of row r = attend) or null
   int32_t* status;                // device status word or null
   const int32_t* work_order;      // optional [num_work] CTA -> work-unit permutation, or null
+  long long* prof;                // cycle-stamp buffer, only used by builds with OMNI_PROFILE
   int BH;
   int N;            // padded sequence length (multiple of 128)
   int seqlen_orig;  // unpadded length
   int nq;           // N / 128
   int max_blocks;
   int num_partial;
-  float scale;       // softmax scale
-  float scale_log2;  // scale * log2(e)
+  float scale;           // softmax scale
+  float scale_log2;      // scale * log2(e)
+  float inv_scale_log2;  // 1 / scale_log2
+  int group_heads;       // heads per scheduling group of the warp-specialised kernel (>= 1)
 };
 
 // Resolve entry `i` of the list of (bh, qb). Returns 0 when the entry is not visited.
@@ -158,10 +161,14 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
-// Running softmax state of one query row (one thread).
+// Running softmax state of one query row (one thread). The reference maximum is kept in the log2
+// domain and is always an integer (the ceiling of scale*log2(e) times the largest raw score seen,
+// moved lazily): exp2(s*c - M) then splits into an exact power of two and a fractional part, which
+// is what lets part of the exponentials be evaluated on the FMA pipe. Any per-row constant factor
+// in P cancels in O = (sum P V) / (sum P); the log-sum-exp is M*ln2 + ln(l).
 struct RowState {
-  float m;  // running max of the raw (unscaled) scores the exponentials are taken against
-  float l;  // running sum of exp2((s - m) * scale_log2)
+  float M;  // integer-valued reference maximum in log2 units, -inf before the first allowed key
+  float l;  // running sum of exp2(s * scale_log2 - M)
 };
 
 // Read the 128 raw scores of this thread's row from TMEM.
@@ -183,56 +190,92 @@ __device__ __forceinline__ void apply_allow(const uint32_t (&allow)[4], float (&
   }
 }
 
-__device__ __forceinline__ float row_max(const float (&s)[128]) {
-  float a = fmaxf(s[0], s[1]), b = fmaxf(s[2], s[3]), c = fmaxf(s[4], s[5]), d = fmaxf(s[6], s[7]);
-#pragma unroll
-  for (int j = 8; j < 128; j += 8) {
-    a = fmaxf(a, fmaxf(s[j], s[j + 1]));
-    b = fmaxf(b, fmaxf(s[j + 2], s[j + 3]));
-    c = fmaxf(c, fmaxf(s[j + 4], s[j + 5]));
-    d = fmaxf(d, fmaxf(s[j + 6], s[j + 7]));
-  }
-  return fmaxf(fmaxf(a, b), fmaxf(c, d));
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
-// Online-softmax update for one tile. `lazy_log2` > 0 keeps the old reference max while the tile
-// max exceeds it by at most that many powers of two (the exponentials then reach 2^lazy_log2,
-// harmless in fp32 sums and in 16-bit P). Returns the factor the O accumulator must be
-// multiplied by before this tile's P*V is added (1 when the reference max did not move).
+__device__ __forceinline__ float row_max(const float (&s)[128]) {
+  float a = s[0], b = s[1], c = s[2], d = s[3];
+#pragma unroll
+  for (int j = 4; j < 124; j += 8) {
+    a = max3(a, s[j], s[j + 1]);
+    b = max3(b, s[j + 2], s[j + 3]);
+    c = max3(c, s[j + 4], s[j + 5]);
+    d = max3(d, s[j + 6], s[j + 7]);
+  }
+  a = max3(a, s[124], s[125]);
+  b = max3(b, s[126], s[127]);
+  return fmaxf(max3(a, b, c), d);
+}
+
+// Online-softmax update for one tile. `lazy_log2` > 0 keeps the old reference maximum while the
+// tile maximum exceeds it by at most that many powers of two (the exponentials then reach
+// 2^lazy_log2, harmless in fp32 sums and in 16-bit P). Returns the factor the O accumulator and
+// the running sum must be multiplied by before this tile is added (1 when the maximum did not move).
 __device__ __forceinline__ float softmax_update(RowState& st, float tile_max, float scale_log2,
                                                 float lazy_log2) {
-  const float m_old = st.m;
-  float m_new = fmaxf(m_old, tile_max);
-  if (lazy_log2 > 0.f && m_old != -INFINITY && (m_new - m_old) * scale_log2 <= lazy_log2) {
-    m_new = m_old;
-  }
+  const float M_old = st.M;
+  float M_new = fmaxf(M_old, ceilf(tile_max * scale_log2));
+  if (lazy_log2 > 0.f && M_old != -INFINITY && M_new - M_old <= lazy_log2) M_new = M_old;
   float alpha = 1.f;
-  if (m_new != m_old) {
-    // m_old == -inf gives exp2(-inf) = 0: nothing accumulated so far survives, which is right.
-    alpha = ex2_approx((m_old - m_new) * scale_log2);
-    st.m = m_new;
+  if (M_new != M_old) {
+    // M_old == -inf gives exp2(-inf) = 0: nothing accumulated so far survives, which is right.
+    alpha = ex2_approx(M_old - M_new);
+    st.M = M_new;
   }
   return alpha;
 }
 
-// P = exp2((s - m) * scale_log2) for the whole row, packed to 16-bit pairs; returns the row sum of
-// the unrounded exponentials. A row with no allowed key in any tile so far has m = -inf: every s
-// is -inf too and all P are 0.
-template <bool BF16>
-__device__ __forceinline__ float exp_and_pack(const float (&s)[128], float m, float scale_log2,
-                                              uint32_t (&pk)[64]) {
-  const float m_use = (m == -INFINITY) ? 0.f : m;
-  const float neg = -m_use * scale_log2;
-  float sum0 = 0.f, sum1 = 0.f;
+// 2^r on [-0.5, 0.5], degree-3 minimax polynomial (max relative error 7.5e-5; P is rounded to
+// 8 or 11 mantissa bits afterwards).
+constexpr float kExp2C0 = 0.9999280571937561f;
+constexpr float kExp2C1 = 0.6932610273361206f;
+constexpr float kExp2C2 = 0.24261116981506348f;
+constexpr float kExp2C3 = 0.0551714189350605f;
+constexpr float kRoundMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds to the nearest integer
+
+// P = exp2(s * scale_log2 - M) for the whole row, packed to 16-bit pairs; returns the row sum of
+// the unrounded exponentials. Packed two-wide fp32 arithmetic throughout. Of every kPolyDen
+// element pairs, kPolyNum are evaluated without the MUFU unit: n = round(x) comes out of one
+// fused multiply-add against the rounding constant, 2^(x-n) from the polynomial, and 2^n is added
+// into the exponent field; the other pairs use ex2.approx. That balances the 16/clk MUFU
+// against the FMA pipe. A row with no allowed key so far has M = -inf and every s = -inf: P is
+// then 0 (MUFU lanes) or below 2^-119 (polynomial lanes, wiped by the next rescale).
+template <bool BF16, int kPolyNum, int kPolyDen>
+__device__ __forceinline__ float exp_and_pack(const float (&s)[128], float M, float scale_log2,
+                                              float inv_scale_log2, uint32_t (&pk)[64]) {
+  const float M_use = (M == -INFINITY) ? 0.f : M;
+  const float2 c2 = make_float2(scale_log2, scale_log2);
+  const float2 negM2 = make_float2(-M_use, -M_use);
+  const float K = kRoundMagic - M_use;  // exact: both are integers below 2^24
+  const float2 K2 = make_float2(K, K);
+  const float2 minus1 = make_float2(-1.f, -1.f);
+  const float s_min = (M_use - 120.f) * inv_scale_log2;  // keeps x >= -120 in the polynomial lanes
+  float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int j = 0; j < 64; ++j) {
-    const float p0 = ex2_approx(fmaf(s[2 * j], scale_log2, neg));
-    const float p1 = ex2_approx(fmaf(s[2 * j + 1], scale_log2, neg));
-    sum0 += p0;
-    sum1 += p1;
-    pk[j] = pack2<BF16>(p0, p1);
+    float2 p2;
+    if ((j % kPolyDen) < kPolyNum) {
+      const float2 s2 = make_float2(fmaxf(s[2 * j], s_min), fmaxf(s[2 * j + 1], s_min));
+      const float2 t2 = __ffma2_rn(s2, c2, K2);          // magic + round(x)
+      const float2 a2 = __ffma2_rn(t2, minus1, K2);      // -(M + round(x))
+      const float2 r2 = __ffma2_rn(s2, c2, a2);          // x - round(x)
+      float2 q2 = __ffma2_rn(r2, make_float2(kExp2C3, kExp2C3), make_float2(kExp2C2, kExp2C2));
+      q2 = __ffma2_rn(q2, r2, make_float2(kExp2C1, kExp2C1));
+      q2 = __ffma2_rn(q2, r2, make_float2(kExp2C0, kExp2C0));
+      p2.x = __int_as_float(__float_as_int(q2.x) + (__float_as_int(t2.x) << 23));
+      p2.y = __int_as_float(__float_as_int(q2.y) + (__float_as_int(t2.y) << 23));
+    } else {
+      const float2 x2 = __ffma2_rn(make_float2(s[2 * j], s[2 * j + 1]), c2, negM2);
+      p2.x = ex2_approx(x2.x);
+      p2.y = ex2_approx(x2.y);
+    }
+    sum2 = __fadd2_rn(sum2, p2);
+    pk[j] = pack2<BF16>(p2.x, p2.y);
   }
-  return sum0 + sum1;
+  return sum2.x + sum2.y;
 }
 
 // Write the packed P row (64 words) to TMEM columns [taddr_row, taddr_row + 64).
@@ -261,12 +304,12 @@ __device__ __forceinline__ void rescale_o(uint32_t taddr_row, float alpha) {
 }
 
 // Final normalisation and store of one output row: O = acc / l (0 when the row attended nothing),
-// LSE = scale * m + ln(l) (-inf when the row attended nothing). `zero_row` forces zeros (padding).
+// LSE = M * ln2 + ln(l) (-inf when the row attended nothing). `zero_row` forces zeros (padding).
 template <int D, bool BF16>
 __device__ __forceinline__ void store_output_row(uint32_t taddr_row, bool have_acc,
                                                  const RowState& st, const FwdParams& p,
                                                  long long row_index, bool zero_row) {
-  const bool empty = zero_row || !have_acc || !(st.l > 0.f);
+  const bool empty = zero_row || !have_acc || st.M == -INFINITY || !(st.l > 0.f);
   const float inv = empty ? 0.f : 1.f / st.l;
   uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(p.o) + row_index * (D * 2));
 #pragma unroll
@@ -292,7 +335,7 @@ __device__ __forceinline__ void store_output_row(uint32_t taddr_row, bool have_a
     }
   }
   if (p.lse != nullptr) {
-    p.lse[row_index] = empty ? -INFINITY : fmaf(st.m, p.scale, __logf(st.l));
+    p.lse[row_index] = empty ? -INFINITY : fmaf(st.M, 0.6931471805599453f, __logf(st.l));
   }
 }
 

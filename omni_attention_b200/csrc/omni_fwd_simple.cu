@@ -133,7 +133,7 @@ omni_fwd_simple_kernel(const __grid_constant__ CUtensorMap tmQ,
     const float alpha = softmax_update(st, row_max(s), p.scale_log2, 0.f);
     if (visited > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) rescale_o<D>(tO + lane_base, alpha);
     uint32_t pk[64];
-    const float sum = exp_and_pack<BF16>(s, st.m, p.scale_log2, pk);
+    const float sum = exp_and_pack<BF16, 0, 1>(s, st.M, p.scale_log2, p.inv_scale_log2, pk);
     st.l = st.l * alpha + sum;
     store_p(tS + lane_base, pk);
     tc_wait_st();

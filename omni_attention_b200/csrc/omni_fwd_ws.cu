@@ -43,6 +43,15 @@ struct WsCfg {
 
 constexpr int kWsThreads = 384;
 constexpr float kLazyRescaleLog2 = 8.f;
+// Share of the exponentials evaluated on the FMA pipe instead of the MUFU unit (pairs per group).
+#ifndef OMNI_POLY_NUM
+#define OMNI_POLY_NUM 0
+#endif
+#ifndef OMNI_POLY_DEN
+#define OMNI_POLY_DEN 1
+#endif
+constexpr int kPolyNum = OMNI_POLY_NUM;
+constexpr int kPolyDen = OMNI_POLY_DEN;
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kWsThreads, 1)
@@ -78,13 +87,19 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int lane = tid & 31;
 
   // ---- which work unit ------------------------------------------------------------------------
-  // Units of one head are adjacent (its K/V stay in L2) and run from the last Q pair to the first:
-  // with causal-like masks the long lists start first and the short ones fill the tail.
   const int npairs = (p.nq + 1) >> 1;
   int unit = blockIdx.x;
   if (p.work_order != nullptr) unit = __ldg(p.work_order + unit);
-  const int bh = unit / npairs;
-  const int pair = npairs - 1 - (unit % npairs);
+  // Heads are taken in groups of `group_heads` (sized on the host so that the K and V of one group
+  // fit in L2 together); inside a group the Q pairs run from last to first with the group's heads
+  // adjacent. With causal-like masks the long lists of all heads of a group start first and the
+  // short ones fill the tail, while co-resident CTAs keep re-reading the same few heads' K/V.
+  const int G = p.group_heads;
+  const int grp = unit / (G * npairs);
+  const int heads_here = min(G, p.BH - grp * G);
+  const int u = unit - grp * G * npairs;
+  const int pair = npairs - 1 - u / heads_here;
+  const int bh = grp * G + u % heads_here;
   const int qbA = 2 * pair;
   const int qbB = 2 * pair + 1;
   const bool haveB = qbB < p.nq;
@@ -201,13 +216,20 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_wait(my_bar_s, cnt & 1, abort_flag, p.status, 10 + g);
       tc_fence_after();
 
+#if defined(OMNI_DEBUG_SKIP_SOFTMAX)
+      // timing experiment only: no softmax work at all, P is whatever S holds
+      tc_fence_before();
+      mbar_arrive(my_bar_p);
+      ++cnt;
+      continue;
+#endif
       float s[128];
       load_scores(tS, s);
       if (masked) apply_allow(allow, s);
       const float alpha = softmax_update(st, row_max(s), p.scale_log2, kLazyRescaleLog2);
       if (cnt > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) rescale_o<D>(tO, alpha);
       uint32_t pk[64];
-      const float sum = exp_and_pack<BF16>(s, st.m, p.scale_log2, pk);
+      const float sum = exp_and_pack<BF16, kPolyNum, kPolyDen>(s, st.M, p.scale_log2, p.inv_scale_log2, pk);
       st.l = st.l * alpha + sum;
       store_p(tS, pk);
       tc_wait_st();
@@ -270,7 +292,15 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       int n_pv[2] = {0, 0};        // P*V products issued per tile (also the P barrier phase count)
       bool q_ready[2] = {false, false};
 
-      auto ring_addr = [&](int fill) { return sRing + (fill % Cfg::kStages) * Cfg::kTileBytes; };
+      // UMMA descriptors are built once; inside the loops a descriptor is "base + constant"
+      // (start-address field, 16-byte units), so issuing one MMA costs a handful of instructions.
+      const uint64_t q_desc[2] = {umma_smem_desc_sw128(sQ0, 16, 1024),
+                                  umma_smem_desc_sw128(sQ0 + Cfg::kTileBytes, 16, 1024)};
+      const uint64_t k_desc0 = umma_smem_desc_sw128(sRing, 16, 1024);                 // K-major view of a ring slot
+      const uint64_t v_desc0 = umma_smem_desc_sw128(sRing, Cfg::kChunkBytes, 1024);   // MN-major view (V)
+      constexpr uint32_t kSlotStep = Cfg::kTileBytes >> 4;
+      constexpr uint32_t kChunkStep = Cfg::kChunkBytes >> 4;
+      auto slot_of = [&](int fill) { return static_cast<uint32_t>(fill % Cfg::kStages); };
       auto wait_full = [&](int fill) {
         mbar_wait(bar_full + 8 * (fill % Cfg::kStages), (fill / Cfg::kStages) & 1, abort_flag, p.status, 30);
       };
@@ -281,24 +311,31 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tc_fence_after();
           q_ready[g] = true;
         }
-        const uint32_t q = sQ0 + g * Cfg::kTileBytes;
-        const uint32_t k = ring_addr(2 * e);
+        const uint64_t qd = q_desc[g];
+        const uint64_t kd = k_desc0 + slot_of(2 * e) * kSlotStep;
+        const uint32_t d_tmem = tS[g];
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * Cfg::kChunkBytes + (ks % 4) * 32;
-          umma_ss(tS[g], umma_smem_desc_sw128(q + off, 16, 1024), umma_smem_desc_sw128(k + off, 16, 1024),
-                  idesc_qk, ks > 0 ? 1u : 0u);
+          // 16 head-dim columns per step: 32 bytes inside a 64-column chunk, chunks kChunkBytes apart
+          const uint32_t off = (ks / 4) * kChunkStep + (ks % 4) * 2;
+          umma_ss(d_tmem, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
         }
         tc_commit(bar_s + 8 * g);
       };
       auto issue_pv = [&](int g, int e) {  // O_g += P_g * V(e)
         mbar_wait(bar_p + 8 * g, n_pv[g] & 1, abort_flag, p.status, 32 + g);
         tc_fence_after();
-        const uint32_t v = ring_addr(2 * e + 1);
+#ifdef OMNI_PROFILE
+        if (p.prof != nullptr && blockIdx.x == 0 && e < 64) p.prof[512 + e * 2 + g] = clock64();
+#endif
+        const uint64_t vd = v_desc0 + slot_of(2 * e + 1) * kSlotStep;
+        const uint32_t d_tmem = tO[g];
+        const uint32_t a_tmem = tS[g];
+        const uint32_t first = n_pv[g] > 0 ? 1u : 0u;
 #pragma unroll
         for (int ks = 0; ks < kBlock / 16; ++ks) {
-          umma_ts(tO[g], tS[g] + 8 * ks, umma_smem_desc_sw128(v + ks * 2048, Cfg::kChunkBytes, 1024),
-                  idesc_pv, (n_pv[g] > 0 || ks > 0) ? 1u : 0u);
+          // 16 keys per step = 16 rows of 128 bytes = 2048 bytes; P advances 8 TMEM columns
+          umma_ts(d_tmem, a_tmem + 8 * ks, vd + ks * 128, idesc_pv, ks > 0 ? 1u : first);
         }
         ++n_pv[g];
       };
@@ -311,19 +348,31 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (tabB[kvb] != 0u) issue_s(1, 0);
         release(0);
       }
+#ifdef OMNI_PROFILE
+#define OMNI_STAMP(i) if (p.prof != nullptr && blockIdx.x == 0 && e < 64) p.prof[e * 8 + (i)] = clock64()
+#else
+#define OMNI_STAMP(i)
+#endif
       for (int e = 0; e < n_sched; ++e) {
         const int kvb = sched[e];
         const bool has_next = e + 1 < n_sched;
         const int kvb_next = has_next ? sched[e + 1] : 0;
+        OMNI_STAMP(0);
         wait_full(2 * e + 1);                 // V(e)
         if (has_next) wait_full(2 * e + 2);   // K(e+1)
         tc_fence_after();
+        OMNI_STAMP(1);
         if (tabA[kvb] != 0u) issue_pv(0, e);
+        OMNI_STAMP(2);
         if (has_next && tabA[kvb_next] != 0u) issue_s(0, e + 1);
+        OMNI_STAMP(3);
         if (tabB[kvb] != 0u) issue_pv(1, e);
+        OMNI_STAMP(4);
         if (has_next && tabB[kvb_next] != 0u) issue_s(1, e + 1);
+        OMNI_STAMP(5);
         release(2 * e + 1);
         if (has_next) release(2 * e + 2);
+        OMNI_STAMP(6);
       }
       tc_commit(bar_done);
       // Keep this thread (and with it the CTA's shared memory and TMEM) alive until every MMA

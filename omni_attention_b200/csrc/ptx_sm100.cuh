@@ -82,6 +82,32 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Warp-collective wait: lane 0 polls (with a short back-off between polls), the other lanes park at
+// the warp barrier. 32 lanes polling the same mbarrier cost shared-memory bandwidth and issue slots
+// that the tensor pipe's operand reads and the MMA-issuing thread need. All 32 lanes must call it.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int32_t* status, int where) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) {
+    ok = mbar_try_wait(bar, parity) != 0;
+    if (!ok && !*abort_flag) {
+      const long long t0 = clock64();
+      while (true) {
+        __nanosleep(32);
+        if (mbar_try_wait(bar, parity)) { ok = true; break; }
+        if (*abort_flag) break;
+        if (clock64() - t0 > kWaitCycleLimit) {
+          *abort_flag = 1;
+          if (status != nullptr) atomicExch(status, kStatusWaitTimeout | (where << 8));
+          break;
+        }
+      }
+    }
+  }
+  __syncwarp();
+  return ok;
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor copy global -> shared, completion on an mbarrier, no multicast)
 // ---------------------------------------------------------------------------------------------

@@ -46,15 +46,17 @@ class OmniAttnError(RuntimeError):
 
 
 def load_library() -> ctypes.CDLL:
-    """Load libomni_attn_sm100.so from the package directory (built by ``omni_attention_b200.build``)."""
+    """Load libomni_attn_sm100.so from the package directory (built by ``omni_attention_b200.build``);
+    the environment variable OMNI_ATTN_LIBRARY names another build of the same library."""
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(_LIB_PATH):
+    path = os.environ.get("OMNI_ATTN_LIBRARY", _LIB_PATH)
+    if not os.path.exists(path):
         raise ImportError(
-            f"{_LIB_PATH} not found: build it with `python -m omni_attention_b200.build` "
+            f"{path} not found: build it with `python -m omni_attention_b200.build` "
             "(there is no fallback implementation)")
-    lib = ctypes.CDLL(_LIB_PATH)
+    lib = ctypes.CDLL(path)
     vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     fwd_args = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp] + [i32] * 10 + [f32, vp, vp]
     for name in ("omni_attn_fwd_sm100", "omni_attn_fwd_simple_sm100"):
