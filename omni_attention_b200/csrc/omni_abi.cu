@@ -231,7 +231,7 @@ int omni_attn_last_cuda_error(void) { return omni::g_last_cuda_error; }
 
 int omni_attn_abi_version(void) { return OMNI_ATTN_ABI_VERSION; }
 
-#ifdef OMNI_PROFILE
+#if defined(OMNI_PROFILE) || defined(OMNI_PROFILE_CTA)
 void omni_attn_debug_set_prof(long long* device_buffer) { omni::g_prof_buffer = device_buffer; }
 #endif
 

@@ -8,7 +8,7 @@
 //   warp  8    TMA producer: Q tiles once, then K,V tiles through a ring of shared-memory stages
 //   warp  9    MMA issuer: tcgen05.mma for S = Q K^T (smem x smem) and O += P V (TMEM x smem)
 //   warps 10-11 idle; they exist so that the third warpgroup can hand its registers to the
-//              softmax groups with setmaxnreg (224 registers per softmax thread, 56 elsewhere)
+//              softmax groups with setmaxnreg (208 registers per softmax thread, 88 elsewhere)
 // TMEM (512 columns): S_A [0,128) S_B [128,256) O_A [256,256+D) O_B [256+D,256+2D). P (16-bit) is
 // written over the first 64 columns of its S.
 //
@@ -42,6 +42,14 @@ struct WsCfg {
 };
 
 constexpr int kWsThreads = 384;
+// Register split made with setmaxnreg. The kernel is compiled for 168 registers per thread (the most
+// 384 threads can have); the increase of the two softmax warpgroups must be covered by the decrease
+// of the third one, or setmaxnreg.inc waits forever.
+constexpr int kLaunchRegs = 168;
+constexpr int kSoftmaxRegs = 208;
+constexpr int kOtherRegs = 88;
+static_assert(2 * kSoftmaxRegs + kOtherRegs <= 3 * kLaunchRegs, "setmaxnreg split exceeds the launch allocation");
+static_assert(kSoftmaxRegs % 8 == 0 && kOtherRegs % 8 == 0, "setmaxnreg counts are multiples of 8");
 constexpr float kLazyRescaleLog2 = 8.f;
 // Share of the exponentials evaluated on the FMA pipe instead of the MUFU unit (pairs per group).
 #ifndef OMNI_POLY_NUM
@@ -85,6 +93,11 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+#ifdef OMNI_PROFILE_CTA
+  auto gtime = [] { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return (long long)t; };
+  long long* crow = p.prof != nullptr ? p.prof + static_cast<long long>(blockIdx.x) * 8 : nullptr;
+  if (tid == 0 && crow) { unsigned sm; asm("mov.u32 %0, %smid;" : "=r"(sm)); crow[0] = gtime(); crow[5] = sm; }
+#endif
 
   // ---- which work unit ------------------------------------------------------------------------
   const int npairs = (p.nq + 1) >> 1;
@@ -180,6 +193,9 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   tc_fence_after();
 
+#ifdef OMNI_PROFILE_CTA
+  if (tid == 0 && crow) { crow[1] = gtime(); crow[6] = *n_sched_slot; crow[7] = cnt_slot[0] + cnt_slot[1]; }
+#endif
   const uint32_t tmem_base = *tmem_slot;
   const int n_sched = *n_sched_slot;
   const int cntA = cnt_slot[0];
@@ -191,7 +207,7 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (warp < 8) {
     // =========================== softmax groups =================================================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
     const int g = warp >> 2;                       // 0 = tile A, 1 = tile B
     const int r = tid & 127;                       // row inside the tile = TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -241,12 +257,15 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_wait(bar_done, 0, abort_flag, p.status, 12 + g);
       tc_fence_after();
     }
+#ifdef OMNI_PROFILE_CTA
+    if (tid == 0 && crow) crow[2] = gtime();
+#endif
     if (g == 0 || haveB) {
       const int q_abs = qb * kBlock + r;
       store_output_row<D, BF16>(tO, my_cnt > 0, st, p, row0 + q_abs, q_abs >= p.seqlen_orig);
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
     if (warp == 8) {
     // =========================== TMA producer ===================================================
     if (lane == 0) {
@@ -305,70 +324,125 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_wait(bar_full + 8 * (fill % Cfg::kStages), (fill / Cfg::kStages) & 1, abort_flag, p.status, 30);
       };
       auto release = [&](int fill) { tc_commit(bar_empty + 8 * (fill % Cfg::kStages)); };
-      auto issue_s = [&](int g, int e) {   // S_g = Q_g * K(e)^T
+      // The tensor pipe accepts a tcgen05.mma only about as fast as it executes them, so the issuing
+      // thread is busy for the whole execution time of a batch and every cycle it then spends
+      // finding out whether the next batch may start (an mbarrier poll is a shared-memory round trip)
+      // is a cycle the pipe idles. The polls for the NEXT batch are therefore started in the middle of
+      // the current one (`peek`, non-blocking) and only fall back to a blocking wait when they failed.
+      // Operand descriptors of a batch are computed before the batch starts, so that each MMA is a
+      // single instruction for this thread: it shares its scheduler partition with two softmax warps
+      // and every extra instruction per MMA waits for an issue slot behind their arithmetic.
+      uint64_t qa[D / 16], qb_[D / 16];
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint32_t off = (ks / 4) * kChunkStep + (ks % 4) * 2;
+        qa[ks] = q_desc[0] + off;
+        qb_[ks] = q_desc[1] + off;
+      }
+      auto issue_s = [&](int g, int e, auto&& peek) {   // S_g = Q_g * K(e)^T
         if (!q_ready[g]) {
           mbar_wait(bar_q + 8 * g, 0, abort_flag, p.status, 31);
           tc_fence_after();
           q_ready[g] = true;
         }
-        const uint64_t qd = q_desc[g];
-        const uint64_t kd = k_desc0 + slot_of(2 * e) * kSlotStep;
-        const uint32_t d_tmem = tS[g];
+        const uint64_t kd0 = k_desc0 + slot_of(2 * e) * kSlotStep;
+        uint64_t kd[D / 16];
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          // 16 head-dim columns per step: 32 bytes inside a 64-column chunk, chunks kChunkBytes apart
-          const uint32_t off = (ks / 4) * kChunkStep + (ks % 4) * 2;
-          umma_ss(d_tmem, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < D / 16; ++ks) kd[ks] = kd0 + ((ks / 4) * kChunkStep + (ks % 4) * 2);
+        const uint32_t d_tmem = tS[g];
+        if (g == 0) {
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            umma_ss(d_tmem, qa[ks], kd[ks], idesc_qk, ks > 0 ? 1u : 0u);
+            if (ks == D / 16 - 4) peek();
+          }
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            umma_ss(d_tmem, qb_[ks], kd[ks], idesc_qk, ks > 0 ? 1u : 0u);
+            if (ks == D / 16 - 4) peek();
+          }
         }
         tc_commit(bar_s + 8 * g);
       };
-      auto issue_pv = [&](int g, int e) {  // O_g += P_g * V(e)
-        mbar_wait(bar_p + 8 * g, n_pv[g] & 1, abort_flag, p.status, 32 + g);
-        tc_fence_after();
-#ifdef OMNI_PROFILE
-        if (p.prof != nullptr && blockIdx.x == 0 && e < 64) p.prof[512 + e * 2 + g] = clock64();
-#endif
-        const uint64_t vd = v_desc0 + slot_of(2 * e + 1) * kSlotStep;
-        const uint32_t d_tmem = tO[g];
-        const uint32_t a_tmem = tS[g];
-        const uint32_t first = n_pv[g] > 0 ? 1u : 0u;
+      auto issue_pv = [&](int g, int e, bool p_ready) {  // O_g += P_g * V(e)
+        // 16 keys per step = 16 rows of 128 bytes = 2048 bytes; P advances 8 TMEM columns
+        const uint64_t vd0 = v_desc0 + slot_of(2 * e + 1) * kSlotStep;
+        uint64_t vd[kBlock / 16];
+        uint32_t pa[kBlock / 16];
 #pragma unroll
         for (int ks = 0; ks < kBlock / 16; ++ks) {
-          // 16 keys per step = 16 rows of 128 bytes = 2048 bytes; P advances 8 TMEM columns
-          umma_ts(d_tmem, a_tmem + 8 * ks, vd + ks * 128, idesc_pv, ks > 0 ? 1u : first);
+          vd[ks] = vd0 + ks * 128;
+          pa[ks] = tS[g] + 8 * ks;
+        }
+        const uint32_t d_tmem = tO[g];
+        const uint32_t first = n_pv[g] > 0 ? 1u : 0u;
+        if (!p_ready) mbar_wait(bar_p + 8 * g, n_pv[g] & 1, abort_flag, p.status, 32 + g);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < kBlock / 16; ++ks) {
+          umma_ts(d_tmem, pa[ks], vd[ks], idesc_pv, ks > 0 ? 1u : first);
         }
         ++n_pv[g];
       };
+      auto peek_full = [&](int fill) -> bool {
+        return mbar_try_wait(bar_full + 8 * (fill % Cfg::kStages), (fill / Cfg::kStages) & 1) != 0;
+      };
+      auto no_peek = [] {};
 
       {  // prologue: scores of the first visited block
         const int kvb = sched[0];
         wait_full(0);
         tc_fence_after();
-        if (tabA[kvb] != 0u) issue_s(0, 0);
-        if (tabB[kvb] != 0u) issue_s(1, 0);
+        if (tabA[kvb] != 0u) issue_s(0, 0, no_peek);
+        if (tabB[kvb] != 0u) issue_s(1, 0, no_peek);
         release(0);
       }
+      bool ring_ok = false;   // V(e) and K(e+1) already seen complete
+      bool pa_ok = false;     // P_A(e) already seen complete
+      for (int e = 0; e < n_sched; ++e) {
+        const int kvb = sched[e];
+        const bool has_next = e + 1 < n_sched;
+        const int kvb_next = has_next ? sched[e + 1] : 0;
+        const bool use_a = tabA[kvb] != 0u, use_b = tabB[kvb] != 0u;
+        const bool next_a = has_next && tabA[kvb_next] != 0u, next_b = has_next && tabB[kvb_next] != 0u;
 #ifdef OMNI_PROFILE
 #define OMNI_STAMP(i) if (p.prof != nullptr && blockIdx.x == 0 && e < 64) p.prof[e * 8 + (i)] = clock64()
 #else
 #define OMNI_STAMP(i)
 #endif
-      for (int e = 0; e < n_sched; ++e) {
-        const int kvb = sched[e];
-        const bool has_next = e + 1 < n_sched;
-        const int kvb_next = has_next ? sched[e + 1] : 0;
         OMNI_STAMP(0);
-        wait_full(2 * e + 1);                 // V(e)
-        if (has_next) wait_full(2 * e + 2);   // K(e+1)
+        if (!ring_ok) {
+          wait_full(2 * e + 1);                 // V(e)
+          if (has_next) wait_full(2 * e + 2);   // K(e+1)
+        }
         tc_fence_after();
+        bool pb_ok = false;
         OMNI_STAMP(1);
-        if (tabA[kvb] != 0u) issue_pv(0, e);
+#ifdef OMNI_PROFILE
+        if (p.prof != nullptr && blockIdx.x == 0 && e < 64) p.prof[512 + e] = (ring_ok ? 1 : 0) | (pa_ok ? 2 : 0);
+#endif
+        if (use_a) issue_pv(0, e, pa_ok);
         OMNI_STAMP(2);
-        if (has_next && tabA[kvb_next] != 0u) issue_s(0, e + 1);
+        if (next_a) {
+          issue_s(0, e + 1, [&] { if (use_b) pb_ok = mbar_try_wait(bar_p + 8, n_pv[1] & 1) != 0; });
+        }
         OMNI_STAMP(3);
-        if (tabB[kvb] != 0u) issue_pv(1, e);
+#ifdef OMNI_PROFILE
+        if (p.prof != nullptr && blockIdx.x == 0 && e < 64) p.prof[512 + e] |= (pb_ok ? 4 : 0);
+#endif
+        if (use_b) issue_pv(1, e, pb_ok);
         OMNI_STAMP(4);
-        if (has_next && tabB[kvb_next] != 0u) issue_s(1, e + 1);
+        ring_ok = false;
+        pa_ok = false;
+        if (next_b) {
+          issue_s(1, e + 1, [&] {
+            bool ok = peek_full(2 * e + 3);                       // V(e+1)
+            if (e + 2 < n_sched) ok = peek_full(2 * e + 4) && ok; // K(e+2)
+            ring_ok = ok;
+            if (next_a) pa_ok = mbar_try_wait(bar_p, n_pv[0] & 1) != 0;
+          });
+        }
         OMNI_STAMP(5);
         release(2 * e + 1);
         if (has_next) release(2 * e + 2);
@@ -384,6 +458,9 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
+#ifdef OMNI_PROFILE_CTA
+  if (tid == 0 && crow) crow[3] = gtime();
+#endif
   if (warp == 9) {
     __syncwarp();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
@@ -398,6 +475,17 @@ static cudaError_t launch_ws_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, c
   static bool attr_done[64] = {};
   cudaError_t e = ensure_smem_attr(kern, Cfg::kSmemBytes, attr_done);
   if (e != cudaSuccess) return e;
+  // The setmaxnreg split inside the kernel is only safe if the kernel was really compiled for
+  // kLaunchRegs registers per thread; refuse to launch otherwise (an unsatisfiable increase would
+  // wait forever).
+  static int num_regs = -1;
+  if (num_regs < 0) {
+    cudaFuncAttributes fa;
+    e = cudaFuncGetAttributes(&fa, kern);
+    if (e != cudaSuccess) return e;
+    num_regs = fa.numRegs;
+  }
+  if (2 * kSoftmaxRegs + kOtherRegs > 3 * num_regs) return cudaErrorLaunchOutOfResources;
   const int npairs = (p.nq + 1) / 2;
   const long long units = static_cast<long long>(npairs) * p.BH;
   kern<<<static_cast<unsigned>(units), kWsThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmK, tmV, p);
