@@ -49,13 +49,15 @@ extern "C" {
 #define OMNI_ERR_ALIGNMENT (-9)        /* q/k/v/o (or a partial mask pool) not 16-byte aligned */
 #define OMNI_ERR_CUDA (-10)            /* a CUDA runtime/driver call failed; see omni_attn_last_cuda_error() */
 #define OMNI_ERR_NO_DRIVER_ENTRY (-11) /* cuTensorMapEncodeTiled is not available from the driver */
+#define OMNI_ERR_SCRATCH (-12)         /* scratch buffer smaller than OMNI_ATTN_SCRATCH_BYTES */
 
 /* Values a kernel can leave in *device_status (0 = clean run). Low byte = kind, upper bits = the
  * place in the kernel that gave up. */
 #define OMNI_STATUS_WAIT_TIMEOUT 1 /* a bounded mbarrier wait ran out; the output is not valid */
 #define OMNI_STATUS_BAD_INDEX 2    /* a kv_indices entry was outside [0, seqlen_padded/128); it was skipped */
 
-/* Forward pass with the warp-specialised kernel.
+/* Forward pass with the warp-specialised, persistent kernel (work units assigned to the resident
+ * CTAs in a fixed pattern; see omni_attn_fwd_scratch_sm100 for dynamic assignment).
  *
  *  q, k, v           [B, H, seqlen_padded, head_dim], contiguous, 16-bit (dtype), device memory
  *  o                 same shape and dtype, written in place (rows >= seqlen_orig are zeroed)
@@ -87,6 +89,23 @@ int omni_attn_fwd_sm100(const void* q, const void* k, const void* v, void* o, fl
                         int B, int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block,
                         int kv_block, int max_blocks, int num_partial, int dtype, float scale,
                         void* cuda_stream, int32_t* device_status_or_null);
+
+/* Same contract and same kernel, with a small scratch buffer in device memory owned by the caller
+ * (at least OMNI_ATTN_SCRATCH_BYTES, 16-byte aligned; contents need not be initialised, the call
+ * clears what it uses on `cuda_stream`). With scratch the resident CTAs take work units from a
+ * shared counter as they become free instead of following a fixed assignment, which balances
+ * masks whose block lists vary unpredictably in length. Two calls that may overlap on the GPU must
+ * not share a scratch buffer. No counterpart in the reference (its grid is one CTA per Q block,
+ * omni-attn-mma/mma/omni_attn_shared_kv.cu:789-790). */
+#define OMNI_ATTN_SCRATCH_BYTES 256
+int omni_attn_fwd_scratch_sm100(const void* q, const void* k, const void* v, void* o, float* lse_or_null,
+                                const int32_t* kv_num_blocks, const int32_t* kv_indices,
+                                const int32_t* block_mask_types, const int32_t* partial_idx_or_null,
+                                const uint8_t* partial_bool_or_null,
+                                const uint32_t* partial_bits_or_null, int B, int H, int seqlen_padded,
+                                int seqlen_orig, int head_dim, int q_block, int kv_block, int max_blocks,
+                                int num_partial, int dtype, float scale, void* cuda_stream,
+                                int32_t* device_status_or_null, void* scratch, long long scratch_bytes);
 
 /* Same contract, computed by the plain one-tile-per-CTA kernel. It takes the place of the
  * reference's correctness-first kernel (omni-attn-mma/mma/attn_naive.cu:305-408). */

@@ -12,7 +12,6 @@ namespace omni {
 namespace {
 
 thread_local int g_last_cuda_error = 0;
-long long* g_prof_buffer = nullptr;  // set only through the OMNI_PROFILE debug entry point
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -78,7 +77,8 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
             const int32_t* kv_num_blocks, const int32_t* kv_indices, const int32_t* types,
             const int32_t* partial_idx, const uint8_t* partial_bool, const uint32_t* partial_bits, int B,
             int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block, int kv_block,
-            int max_blocks, int num_partial, int dtype, float scale, void* stream, int32_t* status) {
+            int max_blocks, int num_partial, int dtype, float scale, void* stream, int32_t* status,
+            void* scratch) {
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || kv_num_blocks == nullptr ||
       kv_indices == nullptr || types == nullptr) {
     return OMNI_ERR_NULL_POINTER;
@@ -98,7 +98,7 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
   const int nq = seqlen_padded / kBlock;
   if (nq > kMaxKvBlocks) return OMNI_ERR_TOO_LONG;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(partial_bool) ||
-      !aligned16(partial_bits)) {
+      !aligned16(partial_bits) || !aligned16(scratch)) {
     return OMNI_ERR_ALIGNMENT;
   }
 
@@ -121,8 +121,9 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
   p.partial_bool = num_partial > 0 ? partial_bool : nullptr;
   p.partial_bits = num_partial > 0 ? partial_bits : nullptr;
   p.status = status;
-  p.work_order = nullptr;
-  p.prof = g_prof_buffer;
+  p.unit_counter = static_cast<int32_t*>(scratch);
+  p.num_units = 0;
+  p.o_aligned32 = (reinterpret_cast<uintptr_t>(o) & 31u) == 0 ? 1 : 0;
   p.BH = static_cast<int>(BH);
   p.N = seqlen_padded;
   p.seqlen_orig = seqlen_orig;
@@ -172,7 +173,23 @@ int omni_attn_fwd_sm100(const void* q, const void* k, const void* v, void* o, fl
   return omni::forward(false, q, k, v, o, lse_or_null, kv_num_blocks, kv_indices, block_mask_types,
                        partial_idx_or_null, partial_bool_or_null, partial_bits_or_null, B, H,
                        seqlen_padded, seqlen_orig, head_dim, q_block, kv_block, max_blocks, num_partial,
-                       dtype, scale, cuda_stream, device_status_or_null);
+                       dtype, scale, cuda_stream, device_status_or_null, nullptr);
+}
+
+int omni_attn_fwd_scratch_sm100(const void* q, const void* k, const void* v, void* o, float* lse_or_null,
+                                const int32_t* kv_num_blocks, const int32_t* kv_indices,
+                                const int32_t* block_mask_types, const int32_t* partial_idx_or_null,
+                                const uint8_t* partial_bool_or_null, const uint32_t* partial_bits_or_null,
+                                int B, int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block,
+                                int kv_block, int max_blocks, int num_partial, int dtype, float scale,
+                                void* cuda_stream, int32_t* device_status_or_null, void* scratch,
+                                long long scratch_bytes) {
+  if (scratch == nullptr) return OMNI_ERR_NULL_POINTER;
+  if (scratch_bytes < OMNI_ATTN_SCRATCH_BYTES) return OMNI_ERR_SCRATCH;
+  return omni::forward(false, q, k, v, o, lse_or_null, kv_num_blocks, kv_indices, block_mask_types,
+                       partial_idx_or_null, partial_bool_or_null, partial_bits_or_null, B, H,
+                       seqlen_padded, seqlen_orig, head_dim, q_block, kv_block, max_blocks, num_partial,
+                       dtype, scale, cuda_stream, device_status_or_null, scratch);
 }
 
 int omni_attn_fwd_simple_sm100(const void* q, const void* k, const void* v, void* o,
@@ -187,7 +204,7 @@ int omni_attn_fwd_simple_sm100(const void* q, const void* k, const void* v, void
   return omni::forward(true, q, k, v, o, lse_or_null, kv_num_blocks, kv_indices, block_mask_types,
                        partial_idx_or_null, partial_bool_or_null, partial_bits_or_null, B, H,
                        seqlen_padded, seqlen_orig, head_dim, q_block, kv_block, max_blocks, num_partial,
-                       dtype, scale, cuda_stream, device_status_or_null);
+                       dtype, scale, cuda_stream, device_status_or_null, nullptr);
 }
 
 int omni_attn_pack_partial_masks_sm100(const uint8_t* partial_bool, uint32_t* partial_bits,
@@ -223,6 +240,7 @@ const char* omni_attn_error_string(int code) {
     case OMNI_ERR_ALIGNMENT: return "q, k, v, o and the partial mask pools must be 16-byte aligned";
     case OMNI_ERR_CUDA: return "a CUDA call failed (see omni_attn_last_cuda_error)";
     case OMNI_ERR_NO_DRIVER_ENTRY: return "cuTensorMapEncodeTiled not available from the CUDA driver";
+    case OMNI_ERR_SCRATCH: return "scratch buffer smaller than OMNI_ATTN_SCRATCH_BYTES";
     default: return "unknown error code";
   }
 }
@@ -231,8 +249,5 @@ int omni_attn_last_cuda_error(void) { return omni::g_last_cuda_error; }
 
 int omni_attn_abi_version(void) { return OMNI_ATTN_ABI_VERSION; }
 
-#if defined(OMNI_PROFILE) || defined(OMNI_PROFILE_CTA)
-void omni_attn_debug_set_prof(long long* device_buffer) { omni::g_prof_buffer = device_buffer; }
-#endif
 
 }  // extern "C"

@@ -40,8 +40,7 @@ struct FwdParams {
   const uint8_t* partial_bool;    // [P, 128, 128] bytes or null
   const uint32_t* partial_bits;   // [P, 128, 4] words (bit c of row r = attend) or null
   int32_t* status;                // device status word or null
-  const int32_t* work_order;      // optional [num_work] CTA -> work-unit permutation, or null
-  long long* prof;                // cycle-stamp buffer, only used by builds with OMNI_PROFILE
+  int32_t* unit_counter;          // zeroed int32 in caller scratch for dynamic unit hand-out, or null
   int BH;
   int N;            // padded sequence length (multiple of 128)
   int seqlen_orig;  // unpadded length
@@ -52,6 +51,8 @@ struct FwdParams {
   float scale_log2;      // scale * log2(e)
   float inv_scale_log2;  // 1 / scale_log2
   int group_heads;       // heads per scheduling group of the warp-specialised kernel (>= 1)
+  int num_units;         // work units of the warp-specialised kernel: ceil(nq / 2) * BH
+  int o_aligned32;       // output base address is 32-byte aligned (256-bit stores allowed)
 };
 
 // Resolve entry `i` of the list of (bh, qb). Returns 0 when the entry is not visited.

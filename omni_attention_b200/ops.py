@@ -30,6 +30,7 @@ _lib = None
 # symbols include/omni_attn_sm100.h declares
 ABI_SYMBOLS = (
     "omni_attn_fwd_sm100",
+    "omni_attn_fwd_scratch_sm100",
     "omni_attn_fwd_simple_sm100",
     "omni_attn_pack_partial_masks_sm100",
     "omni_attn_error_string",
@@ -37,6 +38,7 @@ ABI_SYMBOLS = (
     "omni_attn_abi_version",
 )
 
+SCRATCH_BYTES = 256  # OMNI_ATTN_SCRATCH_BYTES
 STATUS_WAIT_TIMEOUT = 1
 STATUS_BAD_INDEX = 2
 
@@ -63,6 +65,8 @@ def load_library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = fwd_args
         fn.restype = i32
+    lib.omni_attn_fwd_scratch_sm100.argtypes = fwd_args + [vp, ctypes.c_longlong]
+    lib.omni_attn_fwd_scratch_sm100.restype = i32
     lib.omni_attn_pack_partial_masks_sm100.argtypes = [vp, vp, i32, vp]
     lib.omni_attn_pack_partial_masks_sm100.restype = i32
     lib.omni_attn_error_string.argtypes = [i32]
@@ -148,17 +152,36 @@ def omni_attention_forward_out(q: Tensor, k: Tensor, v: Tensor, out: Tensor, blo
     if lse is not None and (lse.dtype != torch.float32 or lse.numel() != B * H * N or not lse.is_contiguous()):
         raise OmniAttnError("lse must be contiguous float32 [B, H, N]")
     lib = load_library()
-    fn = lib.omni_attn_fwd_sm100 if kernel == "ws" else lib.omni_attn_fwd_simple_sm100
-    if kernel not in ("ws", "simple"):
+    if kernel not in ("ws", "ws_static", "simple"):
         raise OmniAttnError(f"unknown kernel {kernel!r}")
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
-        rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _ptr(lse), m["nb"].data_ptr(),
+        args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _ptr(lse), m["nb"].data_ptr(),
                 m["idx"].data_ptr(), m["typ"].data_ptr(), _ptr(m["pidx"]), _ptr(m["pbool"]), _ptr(m["pbits"]),
                 B, H, N, int(seqlen_orig), D, block_mask.Q_BLOCK_SIZE, block_mask.KV_BLOCK_SIZE,
                 int(m["idx"].shape[3]), m["num_partial"], 1 if q.dtype == torch.bfloat16 else 0,
                 float(scale) if scale is not None else 0.0, stream, _ptr(status))
+        if kernel == "ws":
+            # dynamic unit hand-out: one small scratch buffer per (device, stream), reused by every
+            # call on that stream (calls on one stream never overlap)
+            rc = lib.omni_attn_fwd_scratch_sm100(*args, _scratch_for(q.device, stream).data_ptr(), SCRATCH_BYTES)
+        elif kernel == "ws_static":
+            rc = lib.omni_attn_fwd_sm100(*args)
+        else:
+            rc = lib.omni_attn_fwd_simple_sm100(*args)
     _check(rc)
+
+
+_scratch = {}
+
+
+def _scratch_for(device: torch.device, stream: int) -> Tensor:
+    key = (str(device), int(stream))
+    t = _scratch.get(key)
+    if t is None:
+        t = torch.zeros(SCRATCH_BYTES // 4, dtype=torch.int32, device=device)
+        _scratch[key] = t
+    return t
 
 
 def _pad_to_block(x: Tensor, block: int) -> Tuple[Tensor, int]:
