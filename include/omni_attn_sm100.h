@@ -50,6 +50,7 @@ extern "C" {
 #define OMNI_ERR_CUDA (-10)            /* a CUDA runtime/driver call failed; see omni_attn_last_cuda_error() */
 #define OMNI_ERR_NO_DRIVER_ENTRY (-11) /* cuTensorMapEncodeTiled is not available from the driver */
 #define OMNI_ERR_SCRATCH (-12)         /* scratch buffer smaller than OMNI_ATTN_SCRATCH_BYTES */
+#define OMNI_ERR_NOALLOC_LIMIT (-13)   /* omni_attn_fwd_noalloc_sm100: byte mask pool larger than the built-in scratch holds */
 
 /* Values a kernel can leave in *device_status (0 = clean run). Low byte = kind, upper bits = the
  * place in the kernel that gave up. */
@@ -106,6 +107,45 @@ int omni_attn_fwd_scratch_sm100(const void* q, const void* k, const void* v, voi
                                 int seqlen_orig, int head_dim, int q_block, int kv_block, int max_blocks,
                                 int num_partial, int dtype, float scale, void* cuda_stream,
                                 int32_t* device_status_or_null, void* scratch, long long scratch_bytes);
+
+/* Forward pass for callers that have no device memory to hand over and may not allocate any.
+ * This entry point has no counterpart in the reference.
+ *
+ * Who needs it: a plug-in living inside a host program that owns every byte of device memory
+ * through its own allocator and offers plug-ins no way to ask for some (the reference's own
+ * 13-argument binding is such an interface: it has no workspace argument and its contract is that the
+ * callee allocates nothing); a serving loop that must not call cudaMalloc/cudaFree on its hot path
+ * because those calls synchronise the whole device and stall every other stream; a process that has
+ * already given all of its memory budget away.
+ *
+ * Same arguments, results and error codes as omni_attn_fwd_sm100. The scratch that
+ * omni_attn_fwd_scratch_sm100 takes from its caller (the counter from which the resident CTAs draw
+ * work units) is kept in a fixed array inside the library instead, together with room to convert a
+ * byte-per-element partial mask pool to the bit-packed form (one eighth of the mask traffic in
+ * the kernel). The function calls no cudaMalloc, cudaFree or any other allocating routine.
+ *
+ * Limits and rules:
+ *  - the array is OMNI_ATTN_SCRATCH_BYTES + OMNI_ATTN_NOALLOC_MAX_PARTIAL * 2048 bytes (about 2 MB) of
+ *    device memory on every GPU that loads the library, held until the process exits;
+ *  - a byte pool (partial_bool_or_null without partial_bits_or_null) of more than
+ *    OMNI_ATTN_NOALLOC_MAX_PARTIAL tiles is refused with OMNI_ERR_NOALLOC_LIMIT before anything is
+ *    launched; a pool the caller has already bit-packed may have any size;
+ *  - all calls on a device share the one array and it keeps the previous call's contents: each call
+ *    clears the counter and rewrites the packed pool on `cuda_stream` before use. Two calls whose
+ *    GPU work can overlap (different streams without an ordering between them, or different host
+ *    threads on different streams) race on it and must be serialised by the caller;
+ *  - the first call on each device looks up the array's device address (with that device current);
+ *    make that first call before starting any stream capture on the device.
+ */
+#define OMNI_ATTN_NOALLOC_MAX_PARTIAL 1024
+int omni_attn_fwd_noalloc_sm100(const void* q, const void* k, const void* v, void* o, float* lse_or_null,
+                                const int32_t* kv_num_blocks, const int32_t* kv_indices,
+                                const int32_t* block_mask_types, const int32_t* partial_idx_or_null,
+                                const uint8_t* partial_bool_or_null,
+                                const uint32_t* partial_bits_or_null, int B, int H, int seqlen_padded,
+                                int seqlen_orig, int head_dim, int q_block, int kv_block, int max_blocks,
+                                int num_partial, int dtype, float scale, void* cuda_stream,
+                                int32_t* device_status_or_null);
 
 /* Same contract, computed by the plain one-tile-per-CTA kernel. It takes the place of the
  * reference's correctness-first kernel (omni-attn-mma/mma/attn_naive.cu:305-408). */

@@ -4,6 +4,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstdlib>
+#include <mutex>
 
 #include "../../include/omni_attn_sm100.h"
 #include "omni_launch.h"
@@ -226,6 +227,78 @@ int omni_attn_pack_partial_masks_sm100(const uint8_t* partial_bool, uint32_t* pa
   return OMNI_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Forward pass for callers that cannot give the library any device memory to work in.
+//
+// The scratch the persistent kernel wants (the unit counter, and room to bit-pack a byte-per-element
+// partial mask pool) lives in this file-scope device array instead of a caller buffer. Every GPU
+// that loads the library carries the array until the process exits; it is shared by all calls, so
+// it still holds whatever the previous call left there: the counter is cleared at the start of every
+// call and the packed pool is rewritten in full before it is read.
+// ---------------------------------------------------------------------------------------------
+namespace omni {
+namespace {
+
+constexpr long long kBuiltinPoolOffset = OMNI_ATTN_SCRATCH_BYTES;
+constexpr long long kBuiltinScratchBytes =
+    kBuiltinPoolOffset + static_cast<long long>(OMNI_ATTN_NOALLOC_MAX_PARTIAL) * kBlock * 16;
+
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+
+// In host code the array's name is only a handle for the runtime, not a device address; the
+// address has to be asked for, once per device, with that device current.
+int builtin_scratch_address(unsigned char** out) {
+  static std::mutex mu;
+  static unsigned char* addr[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(e);
+    return OMNI_ERR_CUDA;
+  }
+  if (dev < 0 || dev >= 64) return OMNI_ERR_SHAPE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_builtin_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      g_last_cuda_error = static_cast<int>(e);
+      return OMNI_ERR_CUDA;
+    }
+    addr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = addr[dev];
+  return OMNI_OK;
+}
+
+}  // namespace
+}  // namespace omni
+
+int omni_attn_fwd_noalloc_sm100(const void* q, const void* k, const void* v, void* o, float* lse_or_null,
+                                const int32_t* kv_num_blocks, const int32_t* kv_indices,
+                                const int32_t* block_mask_types, const int32_t* partial_idx_or_null,
+                                const uint8_t* partial_bool_or_null, const uint32_t* partial_bits_or_null,
+                                int B, int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block,
+                                int kv_block, int max_blocks, int num_partial, int dtype, float scale,
+                                void* cuda_stream, int32_t* device_status_or_null) {
+  const bool pack_here = num_partial > 0 && partial_bits_or_null == nullptr && partial_bool_or_null != nullptr;
+  if (pack_here && num_partial > OMNI_ATTN_NOALLOC_MAX_PARTIAL) return OMNI_ERR_NOALLOC_LIMIT;
+  unsigned char* scratch = nullptr;
+  int rc = omni::builtin_scratch_address(&scratch);
+  if (rc != OMNI_OK) return rc;
+  const uint32_t* bits = partial_bits_or_null;
+  if (pack_here) {
+    uint32_t* pool = reinterpret_cast<uint32_t*>(scratch + omni::kBuiltinPoolOffset);
+    rc = omni_attn_pack_partial_masks_sm100(partial_bool_or_null, pool, num_partial, cuda_stream);
+    if (rc != OMNI_OK) return rc;
+    bits = pool;
+  }
+  return omni::forward(false, q, k, v, o, lse_or_null, kv_num_blocks, kv_indices, block_mask_types,
+                       partial_idx_or_null, partial_bool_or_null, bits, B, H, seqlen_padded, seqlen_orig,
+                       head_dim, q_block, kv_block, max_blocks, num_partial, dtype, scale, cuda_stream,
+                       device_status_or_null, scratch);
+}
+
 const char* omni_attn_error_string(int code) {
   switch (code) {
     case OMNI_OK: return "ok";
@@ -241,6 +314,9 @@ const char* omni_attn_error_string(int code) {
     case OMNI_ERR_CUDA: return "a CUDA call failed (see omni_attn_last_cuda_error)";
     case OMNI_ERR_NO_DRIVER_ENTRY: return "cuTensorMapEncodeTiled not available from the CUDA driver";
     case OMNI_ERR_SCRATCH: return "scratch buffer smaller than OMNI_ATTN_SCRATCH_BYTES";
+    case OMNI_ERR_NOALLOC_LIMIT:
+      return "byte-per-element partial pool has more than OMNI_ATTN_NOALLOC_MAX_PARTIAL (1024) tiles: too large for "
+             "the built-in scratch; pass a bit-packed pool or use omni_attn_fwd_scratch_sm100";
     default: return "unknown error code";
   }
 }

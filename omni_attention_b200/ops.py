@@ -31,6 +31,7 @@ _lib = None
 ABI_SYMBOLS = (
     "omni_attn_fwd_sm100",
     "omni_attn_fwd_scratch_sm100",
+    "omni_attn_fwd_noalloc_sm100",
     "omni_attn_fwd_simple_sm100",
     "omni_attn_pack_partial_masks_sm100",
     "omni_attn_error_string",
@@ -61,7 +62,7 @@ def load_library() -> ctypes.CDLL:
     lib = ctypes.CDLL(path)
     vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     fwd_args = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp] + [i32] * 10 + [f32, vp, vp]
-    for name in ("omni_attn_fwd_sm100", "omni_attn_fwd_simple_sm100"):
+    for name in ("omni_attn_fwd_sm100", "omni_attn_fwd_simple_sm100", "omni_attn_fwd_noalloc_sm100"):
         fn = getattr(lib, name)
         fn.argtypes = fwd_args
         fn.restype = i32
