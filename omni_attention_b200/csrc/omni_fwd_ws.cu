@@ -33,6 +33,8 @@
 // for the reference's byte-per-element format) before the scores arrive; blocks that are not listed
 // are never loaded. The behaviour replaced is the reference's KV loop
 // (omni-attn-mma/mma/omni_attn_shared_kv.cu:148-559) and epilogue (:560-646).
+#include <type_traits>
+
 #include "omni_common.cuh"
 #include "omni_launch.h"
 
@@ -401,7 +403,10 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           // finding out whether the next batch may start is a cycle the pipe idles. Polls for the
           // NEXT batch are therefore started in the middle of the current one (`peek`, non-blocking)
           // and only fall back to a blocking wait when they failed.
-          auto issue_s = [&](int g, int e, auto&& peek) {   // S_g = Q_g * K(e)^T
+          // The tile index is a compile-time constant (std::integral_constant argument) so that the
+          // per-tile state arrays are indexed statically and stay in registers.
+          auto issue_s = [&](auto gc, int e, auto&& peek) {   // S_g = Q_g * K(e)^T
+            constexpr int g = decltype(gc)::value;
             if (!q_ready[g]) {
               mbar_wait(bar_q + 8 * g, n_q[g] & 1, abort_flag, p.status, 32);
               tc_fence_after();
@@ -420,7 +425,8 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             tc_commit(bar_s + 8 * g);
           };
-          auto issue_pv = [&](int g, int e, bool p_ready) {  // O_g += P_g * V(e)
+          auto issue_pv = [&](auto gc, int e, bool p_ready) {  // O_g += P_g * V(e)
+            constexpr int g = decltype(gc)::value;
             // 16 keys per step = 16 rows of 128 bytes = 2048 bytes; P advances 8 TMEM columns
             const uint64_t vd = v_desc0 + slot_of(2 * e + 1) * kSlotStep;
             const uint32_t a_tmem = tS[g];
@@ -443,14 +449,16 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (n_pv[g] == T->cnt[g]) tc_commit(bar_done + 8 * g);
           };
           auto no_peek = [] {};
+          constexpr std::integral_constant<int, 0> tile_a{};
+          constexpr std::integral_constant<int, 1> tile_b{};
 
           if (n_sched > 0) {
             {  // prologue: scores of the first visited block
               const int kvb = T->sched[0];
               wait_full(0);
               tc_fence_after();
-              if (T->tabA[kvb] != 0u) issue_s(0, 0, no_peek);
-              if (T->tabB[kvb] != 0u) issue_s(1, 0, no_peek);
+              if (T->tabA[kvb] != 0u) issue_s(tile_a, 0, no_peek);
+              if (T->tabB[kvb] != 0u) issue_s(tile_b, 0, no_peek);
               release(0);
               if (n_sched == 1) tc_commit(bar_qfree);
             }
@@ -468,15 +476,15 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               }
               tc_fence_after();
               bool pb_ok = false;
-              if (use_a) issue_pv(0, e, pa_ok);
+              if (use_a) issue_pv(tile_a, e, pa_ok);
               if (next_a) {
-                issue_s(0, e + 1, [&] { if (use_b) pb_ok = mbar_try_wait(bar_p + 8, n_p[1] & 1) != 0; });
+                issue_s(tile_a, e + 1, [&] { if (use_b) pb_ok = mbar_try_wait(bar_p + 8, n_p[1] & 1) != 0; });
               }
-              if (use_b) issue_pv(1, e, pb_ok);
+              if (use_b) issue_pv(tile_b, e, pb_ok);
               ring_ok = false;
               pa_ok = false;
               if (next_b) {
-                issue_s(1, e + 1, [&] {
+                issue_s(tile_b, e + 1, [&] {
                   bool ok = peek_full(2 * e + 3);                       // V(e+1)
                   if (e + 2 < n_sched) ok = peek_full(2 * e + 4) && ok; // K(e+2)
                   ring_ok = ok;
