@@ -279,6 +279,83 @@ __device__ __forceinline__ float exp_and_pack(const float (&s)[128], float M, fl
   return sum2.x + sum2.y;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Half-row (64 score) versions used by the warp-specialised kernel. It makes two passes over the
+// scores in TMEM - first the row maximum, then exponentials - 64 columns at a time, so that only
+// half a row is ever live in registers; re-reading S from TMEM costs a few tens of cycles, keeping
+// all 128 scores plus the packed P in registers costs spills.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void load_scores64(uint32_t taddr_row, float (&s)[64]) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr_row + 32 * c, r);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) s[32 * c + j] = __uint_as_float(r[j]);
+  }
+  tc_wait_ld();
+}
+
+// allow0/allow1: the two allow words of this half (columns [64h, 64h+64)).
+__device__ __forceinline__ void apply_allow64(uint32_t allow0, uint32_t allow1, float (&s)[64]) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) s[j] = ((allow0 >> j) & 1u) ? s[j] : -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) s[32 + j] = ((allow1 >> j) & 1u) ? s[32 + j] : -INFINITY;
+}
+
+__device__ __forceinline__ float row_max64(const float (&s)[64]) {
+  float a = s[0], b = s[1], c = s[2], d = s[3];
+#pragma unroll
+  for (int j = 4; j < 60; j += 8) {
+    a = max3(a, s[j], s[j + 1]);
+    b = max3(b, s[j + 2], s[j + 3]);
+    c = max3(c, s[j + 4], s[j + 5]);
+    d = max3(d, s[j + 6], s[j + 7]);
+  }
+  a = max3(a, s[60], s[61]);
+  b = max3(b, s[62], s[63]);
+  return fmaxf(max3(a, b, c), d);
+}
+
+// exp2(s * scale_log2 - M) for 64 scores -> 32 packed words; returns the sum of the unrounded values.
+// Same arithmetic as exp_and_pack (MUFU ex2 or the FMA-pipe polynomial for kPolyNum of every
+// kPolyDen element pairs).
+template <bool BF16, int kPolyNum, int kPolyDen>
+__device__ __forceinline__ float exp_and_pack64(const float (&s)[64], float M, float scale_log2,
+                                                float inv_scale_log2, uint32_t (&pk)[32]) {
+  const float M_use = (M == -INFINITY) ? 0.f : M;
+  const float2 c2 = make_float2(scale_log2, scale_log2);
+  const float2 negM2 = make_float2(-M_use, -M_use);
+  const float K = kRoundMagic - M_use;
+  const float2 K2 = make_float2(K, K);
+  const float2 minus1 = make_float2(-1.f, -1.f);
+  const float s_min = (M_use - 120.f) * inv_scale_log2;
+  float2 sum2 = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float2 p2;
+    if ((j % kPolyDen) < kPolyNum) {
+      const float2 s2 = make_float2(fmaxf(s[2 * j], s_min), fmaxf(s[2 * j + 1], s_min));
+      const float2 t2 = __ffma2_rn(s2, c2, K2);
+      const float2 a2 = __ffma2_rn(t2, minus1, K2);
+      const float2 r2 = __ffma2_rn(s2, c2, a2);
+      float2 q2 = __ffma2_rn(r2, make_float2(kExp2C3, kExp2C3), make_float2(kExp2C2, kExp2C2));
+      q2 = __ffma2_rn(q2, r2, make_float2(kExp2C1, kExp2C1));
+      q2 = __ffma2_rn(q2, r2, make_float2(kExp2C0, kExp2C0));
+      p2.x = __int_as_float(__float_as_int(q2.x) + (__float_as_int(t2.x) << 23));
+      p2.y = __int_as_float(__float_as_int(q2.y) + (__float_as_int(t2.y) << 23));
+    } else {
+      const float2 x2 = __ffma2_rn(make_float2(s[2 * j], s[2 * j + 1]), c2, negM2);
+      p2.x = ex2_approx(x2.x);
+      p2.y = ex2_approx(x2.y);
+    }
+    sum2 = __fadd2_rn(sum2, p2);
+    pk[j] = pack2<BF16>(p2.x, p2.y);
+  }
+  return sum2.x + sum2.y;
+}
+
 // Write the packed P row (64 words) to TMEM columns [taddr_row, taddr_row + 64).
 __device__ __forceinline__ void store_p(uint32_t taddr_row, const uint32_t (&pk)[64]) {
 #pragma unroll

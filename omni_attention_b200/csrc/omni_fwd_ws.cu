@@ -59,6 +59,15 @@ struct WsCfg {
   static constexpr int kChunkBytes = kBlock * 128;
   static constexpr int kStages = (D == 128) ? 4 : 8;  // ring entries, each one K or one V tile
   static constexpr int kTmemCols = 512;
+  // Softmax shape, chosen by measurement (C4 for D=128, C3 for D=64):
+  //  * D=128: two passes over S in TMEM (row maximum, then exponentials), 64 columns at a time, so that
+  //    half a row is live in registers and nothing spills; all exponentials on the MUFU unit (any share
+  //    moved to the FMA pipe slows the MMA-issuing thread more than it saves).
+  //  * D=64: one pass with the whole row in registers, a quarter of the exponentials evaluated by a
+  //    polynomial on the FMA pipe (the MMAs are half as long, MUFU is the scarcer unit).
+  static constexpr bool kTwoPass = (D == 128);
+  static constexpr int kPolyNum = (D == 128) ? 0 : 1;   // element pairs per group of kPolyDen on the FMA pipe
+  static constexpr int kPolyDen = (D == 128) ? 1 : 4;
   // q_full[2] q_free ring_full[S] ring_empty[S] s_full[2] p_ready[2] done[2] o_free[2] tab_full[2] tab_empty[2] near_end
   static constexpr int kNumBars = 3 + 2 * kStages + 13;
   static constexpr int kTableBytes = 2 * static_cast<int>(sizeof(UnitTable));
@@ -81,16 +90,6 @@ constexpr float kLazyRescaleLog2 = 8.f;
 // of the current one: early enough for the next unit's tables to be ready before the loads run dry,
 // late enough that a CTA does not sit on a long unit while other CTAs have already run out of work.
 constexpr int kNearEndBlocks = 12;
-// Share of the exponentials evaluated on the FMA pipe instead of the MUFU unit (pairs per group).
-#ifndef OMNI_POLY_NUM
-#define OMNI_POLY_NUM 0
-#endif
-#ifndef OMNI_POLY_DEN
-#define OMNI_POLY_DEN 1
-#endif
-constexpr int kPolyNum = OMNI_POLY_NUM;
-constexpr int kPolyDen = OMNI_POLY_DEN;
-
 // Unit index -> (batch*head, Q pair). The order is chosen for two things at once.
 //  * The first quarter of the Q pairs (for causal-like masks: the shortest lists) of ALL heads comes
 //    last, so that the tail of the grid is filled with short units; everything else comes first.
@@ -244,15 +243,41 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after();
         if (cnt == 0) { OMNI_USTAMP(2); }
 
+        if constexpr (Cfg::kTwoPass) {
+        // pass 1: row maximum, 64 columns at a time
+        float mx = -INFINITY;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float s[64];
+          load_scores64(tS + 64 * h, s);
+          if (masked) apply_allow64(allow[2 * h], allow[2 * h + 1], s);
+          mx = fmaxf(mx, row_max64(s));
+        }
+        const float alpha = softmax_update(st, mx, p.scale_log2, kLazyRescaleLog2);
+        if (cnt > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) rescale_o<D>(tO, alpha);
+        // pass 2: exponentials; P half h (32 words) lands on columns that were read in pass 2 already
+        float sum = 0.f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float s[64];
+          load_scores64(tS + 64 * h, s);
+          if (masked) apply_allow64(allow[2 * h], allow[2 * h + 1], s);
+          uint32_t pk[32];
+          sum += exp_and_pack64<BF16, Cfg::kPolyNum, Cfg::kPolyDen>(s, st.M, p.scale_log2, p.inv_scale_log2, pk);
+          tmem_st32(tS + 32 * h, pk);
+        }
+        st.l = st.l * alpha + sum;
+        } else {
         float s[128];
         load_scores(tS, s);
         if (masked) apply_allow(allow, s);
         const float alpha = softmax_update(st, row_max(s), p.scale_log2, kLazyRescaleLog2);
         if (cnt > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) rescale_o<D>(tO, alpha);
         uint32_t pk[64];
-        const float sum = exp_and_pack<BF16, kPolyNum, kPolyDen>(s, st.M, p.scale_log2, p.inv_scale_log2, pk);
+        const float sum = exp_and_pack<BF16, Cfg::kPolyNum, Cfg::kPolyDen>(s, st.M, p.scale_log2, p.inv_scale_log2, pk);
         st.l = st.l * alpha + sum;
         store_p(tS, pk);
+        }
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(my_bar_p);
