@@ -60,8 +60,8 @@ struct WsCfg {
   static constexpr int kStages = (D == 128) ? 4 : 8;  // ring entries, each one K or one V tile
   static constexpr int kTmemCols = 512;
   // Softmax shape, chosen by measurement (C4 for D=128, C3 for D=64):
-  //  * D=128: two passes over S in TMEM (row maximum, then exponentials), 64 columns at a time, so that
-  //    half a row is live in registers and nothing spills; all exponentials on the MUFU unit (any share
+  //  * D=128: two passes over S in TMEM (row maximum over the whole row, then exponentials 64 columns at
+  //    a time), so that the scores and the packed P are never live together and nothing spills; all exponentials on the MUFU unit (any share
   //    moved to the FMA pipe slows the MMA-issuing thread more than it saves).
   //  * D=64: one pass with the whole row in registers, a quarter of the exponentials evaluated by a
   //    polynomial on the FMA pipe (the MMAs are half as long, MUFU is the scarcer unit).
@@ -244,14 +244,13 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (cnt == 0) { OMNI_USTAMP(2); }
 
         if constexpr (Cfg::kTwoPass) {
-        // pass 1: row maximum, 64 columns at a time
-        float mx = -INFINITY;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          float s[64];
-          load_scores64(tS + 64 * h, s);
-          if (masked) apply_allow64(allow[2 * h], allow[2 * h + 1], s);
-          mx = fmaxf(mx, row_max64(s));
+        // pass 1: row maximum over the whole row (the scores are dropped again right away)
+        float mx;
+        {
+          float s[128];
+          load_scores(tS, s);
+          if (masked) apply_allow(allow, s);
+          mx = row_max(s);
         }
         const float alpha = softmax_update(st, mx, p.scale_log2, kLazyRescaleLog2);
         if (cnt > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) rescale_o<D>(tO, alpha);
