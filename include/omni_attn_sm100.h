@@ -165,6 +165,33 @@ int omni_attn_fwd_simple_sm100(const void* q, const void* k, const void* v, void
 int omni_attn_pack_partial_masks_sm100(const uint8_t* partial_bool, uint32_t* partial_bits,
                                        int num_partial, void* cuda_stream);
 
+/* Builds the block mask of an interleaved text / image sequence on the GPU, in the reference's
+ * metadata format, from the image span positions. Replaces the host-side builder
+ * create_omni_block_mask_from_modality_positions (omni-attn-mma/omni_attn_torch.py:1518-1736) together
+ * with the dense mask (transfusion_pytorch/transfusion.py:496-515) and build_partial_block_data
+ * (omni-attn-mma/omni_attn_torch.py:148-205) it relies on. Mask rule: key k is attended by query q iff
+ * k <= q, or q >= offset_m and k < offset_m + length_m for some span m; nothing at or beyond `seqlen`.
+ *
+ *  modality_positions  [B, M, 3] int32 (type, offset, length), device; entries with length <= 0 are ignored
+ *  seqlen              unpadded length; seqlen_padded = multiple of 128 >= seqlen (nq = seqlen_padded / 128)
+ *  kv_num_blocks       out [B, H, nq];  kv_indices, block_mask_types, partial_idx  out [B, H, nq, nq]
+ *                      (listed blocks first, ascending; the same lists for every head of a batch element)
+ *  partial_bits        out [partial_capacity, 128, 4] bit-packed PARTIAL tiles (pool shared by the heads)
+ *  partial_bool_or_null  out [partial_capacity, 128, 128] bytes, the reference's form, or NULL
+ *  num_partial_out     out, one device int32: PARTIAL tiles the mask needs; when it exceeds
+ *                      partial_capacity the tiles beyond the capacity were not written and the call must
+ *                      be repeated with a larger pool
+ *  scratch             device memory, at least 2 * B * nq * 4 bytes
+ * Block types by content: all elements allowed -> FULL, none -> not listed, a diagonal block of plain
+ * causal rows -> CAUSAL, anything else -> PARTIAL (the derivation of
+ * omni-attn-mma/generate_attn_data.py:200-236; the reference builder's "dominant type" shortcut types
+ * some fully allowed blocks PARTIAL with an all-true mask, which expands to the same dense mask). */
+int omni_attn_build_mask_sm100(const int32_t* modality_positions, int B, int M, int H, int seqlen,
+                               int seqlen_padded, int32_t* kv_num_blocks, int32_t* kv_indices,
+                               int32_t* block_mask_types, int32_t* partial_idx, uint32_t* partial_bits,
+                               uint8_t* partial_bool_or_null, int partial_capacity, int32_t* num_partial_out,
+                               void* scratch, long long scratch_bytes, void* cuda_stream);
+
 /* Text for an OMNI_ERR_* code; the pointer is static storage. */
 const char* omni_attn_error_string(int code);
 

@@ -7,13 +7,15 @@ Public surface (mirrors the reference's operator module omni-attn-mma/omni_attn_
                                 points) importable, so the reference's own wrappers run on these kernels
 """
 from .block_mask import (BlockMaskType, OmniBlockMask, block_mask_from_dense, block_mask_from_row_limits,
-                         build_partial_block_data, create_causal_omni_block_mask, dense_mask_from_blocks,
+                         build_partial_block_data, create_causal_omni_block_mask,
+                         create_omni_block_mask_from_modality_positions, dense_mask_from_blocks,
                          row_limits_from_modality_positions)
 from .ops import OmniAttnError, omni_attention, omni_attention_forward_out, pack_partial_masks
 
 __all__ = [
     "BlockMaskType", "OmniBlockMask", "block_mask_from_dense", "block_mask_from_row_limits",
-    "build_partial_block_data", "create_causal_omni_block_mask", "dense_mask_from_blocks",
+    "build_partial_block_data", "create_causal_omni_block_mask", "create_omni_block_mask_from_modality_positions",
+    "dense_mask_from_blocks",
     "row_limits_from_modality_positions", "OmniAttnError", "omni_attention", "omni_attention_forward_out",
     "pack_partial_masks", "install_reference_module",
 ]

@@ -346,3 +346,53 @@ def row_limits_from_modality_positions(seq_len: int, modality_positions: Sequenc
                 limits[b, lo:hi] = torch.maximum(limits[b, lo:hi], torch.tensor(hi - 1, device=device))
                 causal_rows[b, lo:hi] = False
     return limits, causal_rows
+
+
+def _limits_from_modality_tensor(modality_positions: Tensor, seq_len: int, padded: int) -> Tuple[Tensor, Tensor]:
+    """Row limits (-1 on padding rows) and plain-causal-row flags for a [B, M, 3] (type, offset, length) tensor."""
+    mp = modality_positions.detach().cpu().long()
+    B = mp.shape[0]
+    q = torch.arange(padded).view(1, padded)
+    limits = q.repeat(B, 1)
+    plain = torch.ones(B, padded, dtype=torch.bool)
+    for m in range(mp.shape[1]):
+        off, ln = mp[:, m, 1].view(B, 1), mp[:, m, 2].view(B, 1)
+        started = (ln > 0) & (q >= off)
+        limits = torch.where(started, torch.maximum(limits, off + ln - 1), limits)
+        plain &= ~(started & (q < off + ln))
+    limits = limits.clamp(max=seq_len - 1)
+    pad = q >= seq_len
+    limits = torch.where(pad, torch.full_like(limits, -1), limits)
+    plain &= ~pad
+    return limits, plain
+
+
+def create_omni_block_mask_from_modality_positions(modality_positions: Tensor, batch: int, nheads: int, q_len: int,
+                                                   kv_len: int, Q_BLOCK_SIZE: int = 128, KV_BLOCK_SIZE: int = 128,
+                                                   device="cpu") -> OmniBlockMask:
+    """Block mask of an interleaved text / image sequence from ``modality_positions`` [B, M, 3] =
+    (type, offset, length); same name, arguments and padding behaviour as the reference's builder
+    (omni-attn-mma/omni_attn_torch.py:1518-1736).
+
+    The dense mask it stands for is the reference's: key <= query, or query >= offset and key <
+    offset + length for some span (transfusion_pytorch/transfusion.py:496-515); nothing at or beyond the
+    unpadded length. Blocks are typed by content (all allowed -> FULL, none -> not listed, a diagonal
+    block of plain causal rows -> CAUSAL, else PARTIAL); the reference types some fully allowed blocks
+    PARTIAL with an all-true tile, which expands to the same dense mask. The PARTIAL pool is shared by
+    the heads of a batch element. On a CUDA device the mask is built by the library's kernels and stays
+    on the device; on the CPU it is built with tensor arithmetic. Neither builds an N x N tensor.
+    """
+    if q_len != kv_len:
+        raise ValueError("Q_len must equal KV_len")
+    if Q_BLOCK_SIZE != 128 or KV_BLOCK_SIZE != 128:
+        raise ValueError("Unsupported block size: Q_BLOCK_SIZE and KV_BLOCK_SIZE must be 128.")
+    if modality_positions.dim() != 3 or modality_positions.shape[0] != batch or modality_positions.shape[2] != 3:
+        raise ValueError("modality_positions must be [batch, M, 3]")
+    padded = -(-q_len // 128) * 128
+    dev = torch.device(device)
+    if dev.type == "cuda":
+        from .ops import build_block_mask_cuda
+
+        return build_block_mask_cuda(modality_positions, batch, nheads, q_len, padded, dev)
+    limits, plain = _limits_from_modality_tensor(modality_positions, q_len, padded)
+    return block_mask_from_row_limits(limits, nheads, plain, 128, True).to(dev)

@@ -34,6 +34,7 @@ ABI_SYMBOLS = (
     "omni_attn_fwd_noalloc_sm100",
     "omni_attn_fwd_simple_sm100",
     "omni_attn_pack_partial_masks_sm100",
+    "omni_attn_build_mask_sm100",
     "omni_attn_error_string",
     "omni_attn_last_cuda_error",
     "omni_attn_abi_version",
@@ -70,6 +71,9 @@ def load_library() -> ctypes.CDLL:
     lib.omni_attn_fwd_scratch_sm100.restype = i32
     lib.omni_attn_pack_partial_masks_sm100.argtypes = [vp, vp, i32, vp]
     lib.omni_attn_pack_partial_masks_sm100.restype = i32
+    lib.omni_attn_build_mask_sm100.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp,
+                                               ctypes.c_longlong, vp]
+    lib.omni_attn_build_mask_sm100.restype = i32
     lib.omni_attn_error_string.argtypes = [i32]
     lib.omni_attn_error_string.restype = ctypes.c_char_p
     lib.omni_attn_last_cuda_error.argtypes = []
@@ -103,6 +107,47 @@ def pack_partial_masks(partial_block_masks: Tensor) -> Tensor:
             stream = torch.cuda.current_stream().cuda_stream
             _check(load_library().omni_attn_pack_partial_masks_sm100(src.data_ptr(), bits.data_ptr(), P, stream))
     return bits
+
+
+def build_block_mask_cuda(modality_positions: Tensor, batch: int, nheads: int, seq_len: int, padded: int,
+                          device: torch.device) -> OmniBlockMask:
+    """Runs omni_attn_build_mask_sm100 on ``device`` and wraps its outputs in an OmniBlockMask whose
+    tensors stay on the device. The PARTIAL pool is sized from the number of spans (every span start
+    or end can make at most one Q block row and one KV block column of tiles partial) and the call is
+    repeated once with the exact size if that guess was too small."""
+    lib = load_library()
+    mp = modality_positions.to(device=device, dtype=torch.int32).contiguous()
+    M = int(mp.shape[1])
+    nq = padded // 128
+    nb = torch.empty(batch, nheads, nq, dtype=torch.int32, device=device)
+    idx = torch.empty(batch, nheads, nq, nq, dtype=torch.int32, device=device)
+    typ = torch.empty_like(idx)
+    pidx = torch.empty_like(idx)
+    count = torch.zeros(1, dtype=torch.int32, device=device)
+    scratch = torch.empty(2 * batch * nq, dtype=torch.int32, device=device)
+    capacity = max(16, batch * (2 * M + 2) * 4)
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream().cuda_stream
+        while True:
+            bits = torch.empty(capacity, 128, 4, dtype=torch.int32, device=device)
+            _check(lib.omni_attn_build_mask_sm100(_ptr(mp), batch, M, nheads, int(seq_len), int(padded), nb.data_ptr(),
+                                                  idx.data_ptr(), typ.data_ptr(), pidx.data_ptr(), bits.data_ptr(), None,
+                                                  capacity, count.data_ptr(), scratch.data_ptr(), scratch.numel() * 4,
+                                                  stream))
+            need = int(count.item())
+            if need <= capacity:
+                break
+            capacity = need
+    bits = bits[:need].contiguous()
+    # the container's pool field is the reference's bool [P,128,128]; expand the bit tiles once
+    w = bits.to(torch.int64) & 0xFFFFFFFF
+    pool = ((w.unsqueeze(-1) >> torch.arange(32, device=device)) & 1).bool().view(need, 128, 128)
+    bm = OmniBlockMask(nb, idx, typ, padded, padded, 128, 128, pidx, pool)
+    for pack in (True, False):
+        bm._cache[(str(device), pack)] = {"nb": nb, "idx": idx, "typ": typ, "pidx": pidx,
+                                          "pbool": None if pack or need == 0 else pool,
+                                          "pbits": bits if pack and need > 0 else None, "num_partial": need}
+    return bm
 
 
 def _device_mask(bm: OmniBlockMask, device: torch.device, pack_bits: bool) -> dict:

@@ -138,3 +138,22 @@ def test_builders_against_reference_in_process():
     idx, pool = ref.build_partial_block_data(g["bm"], g["dense"])
     mi, mp = build_partial_block_data(g["bm"], g["dense"])
     assert torch.equal(idx, mi) and torch.equal(pool, mp)
+
+
+@pytest.mark.parametrize("seq_len", [1000, 1024])
+def test_mask_from_modality_positions_matches_dense_rule(seq_len):
+    """CPU builder with the reference's name and arguments against the oracle's restatement of the
+    dense rule (transfusion_pytorch/transfusion.py:496-515), with and without padding."""
+    from omni_attention_b200 import create_omni_block_mask_from_modality_positions
+
+    mp = torch.tensor([[[1, 100, 256], [1, 600, 130], [0, 0, 0]], [[1, 0, 128], [1, 128, 128], [1, 700, 300]]])
+    bm = create_omni_block_mask_from_modality_positions(mp, 2, 3, seq_len, seq_len)
+    pad = -(-seq_len // 128) * 128
+    assert (bm.q_len, bm.kv_len) == (pad, pad) and bm.kv_num_blocks.shape == (2, 3, pad // 128)
+    want = torch.zeros(2, pad, pad, dtype=torch.bool)
+    want[:, :seq_len, :seq_len] = orc.naive_attn_mask(seq_len, mp)
+    got = bm.to_dense_mask()
+    for h in range(3):
+        assert torch.equal(got[:, h], want)
+    with pytest.raises(ValueError):
+        create_omni_block_mask_from_modality_positions(mp, 2, 3, 512, 256)

@@ -276,3 +276,79 @@ def test_reference_pybind_surface(cuda_device):
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     assert float((lse.cpu() - gc["lse"]).abs().max()) <= LSE_ATOL
+
+
+def _random_modality_positions(B, N, gen, max_spans=6):
+    rows = []
+    for _ in range(B):
+        spans, pos = [], 0
+        for _ in range(max_spans):
+            pos += int(torch.randint(1, max(2, N // 8), (1,), generator=gen))
+            ln = int(torch.randint(1, max(2, N // 5), (1,), generator=gen))
+            if pos + ln > N:
+                break
+            spans.append([1, pos, ln])
+            pos += ln
+        spans += [[0, 0, 0]] * (max_spans - len(spans))
+        rows.append(spans)
+    return torch.tensor(rows, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("seq_len", [500, 1024, 4096])
+def test_gpu_mask_builder_matches_cpu_builder_and_dense_rule(cuda_device, seq_len):
+    """omni_attn_build_mask_sm100 (through the package's builder on a CUDA device) against the CPU
+    builder: same lists and types, same dense expansion, and attention on the GPU-built mask against
+    the oracle."""
+    from omni_attention_b200 import create_omni_block_mask_from_modality_positions as build
+
+    g = torch.Generator().manual_seed(seq_len)
+    B, H, D = 2, 2, 64
+    mp = _random_modality_positions(B, seq_len, g)
+    cpu = build(mp, B, H, seq_len, seq_len)
+    gpu = build(mp, B, H, seq_len, seq_len, device=cuda_device)
+    assert gpu.kv_indices.is_cuda and gpu.q_len == cpu.q_len
+    assert torch.equal(gpu.kv_num_blocks.cpu(), cpu.kv_num_blocks)
+    assert torch.equal(gpu.kv_indices.cpu(), cpu.kv_indices)
+    assert torch.equal(gpu.block_mask_types.cpu(), cpu.block_mask_types)
+    assert gpu.partial_block_masks.shape == cpu.partial_block_masks.shape
+    # pool numbering may differ; the tile each entry points at must not
+    sel = cpu.partial_block_mask_indices >= 0
+    assert torch.equal(gpu.partial_block_mask_indices.cpu() >= 0, sel)
+    ct = cpu.partial_block_masks[cpu.partial_block_mask_indices[sel].long()]
+    gt = gpu.partial_block_masks.cpu()[gpu.partial_block_mask_indices.cpu()[sel].long()]
+    assert torch.equal(ct, gt)
+    if seq_len <= 1024:
+        pad = cpu.q_len
+        want = torch.zeros(B, pad, pad, dtype=torch.bool)
+        want[:, :seq_len, :seq_len] = orc.naive_attn_mask(seq_len, mp.long())
+        assert torch.equal(gpu.to(torch.device("cpu")).to_dense_mask()[:, 0], want)
+    q, k, v = (torch.randn(B, H, seq_len, D, generator=g).bfloat16() for _ in range(3))
+    out, lse = omni_attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), gpu, return_lse=True, check_status=True)
+    pad = lambda t: torch.nn.functional.pad(t, (0, 0, 0, cpu.q_len - seq_len))
+    ref_out, ref_lse = orc.block_mask_attention(pad(q), pad(k), pad(v), cpu, seqlen_orig=seq_len)
+    assert_parity(out, lse, ref_out[:, :, :seq_len], ref_lse[:, :, :seq_len], f"gpu-built mask N={seq_len}")
+
+
+def test_gpu_mask_builder_at_c5_size(cuda_device):
+    """The 32K multi-image layout: GPU-built mask equals the CPU-built one; prints the build time."""
+    from omni_attention_b200 import create_omni_block_mask_from_modality_positions as build
+
+    cfg = inputs.CONFIGS["C5"]
+    cpu, meta = inputs.make_block_mask(cfg, seed=0)
+    spans = meta["image_spans"]
+    M = max(len(s) for s in spans)
+    mp = torch.tensor([[[1, o, l] for o, l in s] + [[0, 0, 0]] * (M - len(s)) for s in spans], dtype=torch.int32)
+    gpu = build(mp, cfg.B, cfg.H, cfg.N, cfg.N, device=cuda_device)
+    assert torch.equal(gpu.kv_num_blocks.cpu(), cpu.kv_num_blocks)
+    assert torch.equal(gpu.kv_indices.cpu(), cpu.kv_indices)
+    assert torch.equal(gpu.block_mask_types.cpu(), cpu.block_mask_types)
+    assert gpu.partial_block_masks.shape[0] == cpu.partial_block_masks.shape[0]
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        build(mp, cfg.B, cfg.H, cfg.N, cfg.N, device=cuda_device)
+    e1.record()
+    torch.cuda.synchronize()
+    out_bytes = 4 * (3 * cpu.kv_indices.numel() + cpu.kv_num_blocks.numel())
+    print(f"C5 mask build (incl. host sync and bit expansion): {e0.elapsed_time(e1) / 5:.3f} ms, index tensors {out_bytes / 1e6:.0f} MB")
