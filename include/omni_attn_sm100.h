@@ -50,6 +50,7 @@ extern "C" {
 #define OMNI_ERR_CUDA (-10)            /* a CUDA runtime/driver call failed; see omni_attn_last_cuda_error() */
 #define OMNI_ERR_NO_DRIVER_ENTRY (-11) /* cuTensorMapEncodeTiled is not available from the driver */
 #define OMNI_ERR_SCRATCH (-12)         /* scratch buffer smaller than OMNI_ATTN_SCRATCH_BYTES */
+#define OMNI_ERR_SOFTCAP (-14)         /* softcap negative or NaN */
 #define OMNI_ERR_NOALLOC_LIMIT (-13)   /* omni_attn_fwd_noalloc_sm100: byte mask pool larger than the built-in scratch holds */
 
 /* Values a kernel can leave in *device_status (0 = clean run). Low byte = kind, upper bits = the
@@ -107,6 +108,22 @@ int omni_attn_fwd_scratch_sm100(const void* q, const void* k, const void* v, voi
                                 int seqlen_orig, int head_dim, int q_block, int kv_block, int max_blocks,
                                 int num_partial, int dtype, float scale, void* cuda_stream,
                                 int32_t* device_status_or_null, void* scratch, long long scratch_bytes);
+
+/* Extended forward: everything omni_attn_fwd_sm100 does, plus
+ *  softcap   > 0: the scaled scores go through softcap * tanh(x / softcap) before masking, the
+ *            score_mod of the Transfusion attention (transfusion_pytorch/transfusion.py:358-364, applied
+ *            at :953-961 and :967 with softcap_value = 50); 0 = none. The reference's kernels have no
+ *            soft-cap.
+ *  scratch_or_null / scratch_bytes   as in omni_attn_fwd_scratch_sm100, or NULL for the fixed unit
+ *            assignment. */
+int omni_attn_fwd_ex_sm100(const void* q, const void* k, const void* v, void* o, float* lse_or_null,
+                           const int32_t* kv_num_blocks, const int32_t* kv_indices,
+                           const int32_t* block_mask_types, const int32_t* partial_idx_or_null,
+                           const uint8_t* partial_bool_or_null, const uint32_t* partial_bits_or_null, int B,
+                           int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block, int kv_block,
+                           int max_blocks, int num_partial, int dtype, float scale, void* cuda_stream,
+                           int32_t* device_status_or_null, float softcap, void* scratch_or_null,
+                           long long scratch_bytes);
 
 /* Forward pass for callers that have no device memory to hand over and may not allocate any.
  * This entry point has no counterpart in the reference.

@@ -79,7 +79,7 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
             const int32_t* partial_idx, const uint8_t* partial_bool, const uint32_t* partial_bits, int B,
             int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block, int kv_block,
             int max_blocks, int num_partial, int dtype, float scale, void* stream, int32_t* status,
-            void* scratch) {
+            void* scratch, float softcap = 0.f) {
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || kv_num_blocks == nullptr ||
       kv_indices == nullptr || types == nullptr) {
     return OMNI_ERR_NULL_POINTER;
@@ -94,6 +94,7 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
   const long long BH = static_cast<long long>(B) * H;
   const long long rows = BH * seqlen_padded;
   if (rows >= (1LL << 31) || BH > 65535) return OMNI_ERR_SHAPE;
+  if (simple && softcap > 0.f) return OMNI_ERR_SOFTCAP;
   if (num_partial < 0) return OMNI_ERR_PARTIAL;
   if (num_partial > 0 && partial_bool == nullptr && partial_bits == nullptr) return OMNI_ERR_PARTIAL;
   const int nq = seqlen_padded / kBlock;
@@ -134,6 +135,8 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
   p.scale = scale > 0.f ? scale : 1.f / std::sqrt(static_cast<float>(head_dim));
   p.scale_log2 = p.scale * 1.4426950408889634f;
   p.inv_scale_log2 = 1.f / p.scale_log2;
+  p.cap_in = softcap > 0.f ? p.scale / softcap : 0.f;
+  p.cap_out = softcap > 0.f ? softcap / p.scale : 0.f;
   p.group_heads = group_heads_for(BH, seqlen_padded, head_dim);
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -191,6 +194,22 @@ int omni_attn_fwd_scratch_sm100(const void* q, const void* k, const void* v, voi
                        partial_idx_or_null, partial_bool_or_null, partial_bits_or_null, B, H,
                        seqlen_padded, seqlen_orig, head_dim, q_block, kv_block, max_blocks, num_partial,
                        dtype, scale, cuda_stream, device_status_or_null, scratch);
+}
+
+int omni_attn_fwd_ex_sm100(const void* q, const void* k, const void* v, void* o, float* lse_or_null,
+                           const int32_t* kv_num_blocks, const int32_t* kv_indices,
+                           const int32_t* block_mask_types, const int32_t* partial_idx_or_null,
+                           const uint8_t* partial_bool_or_null, const uint32_t* partial_bits_or_null, int B,
+                           int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block, int kv_block,
+                           int max_blocks, int num_partial, int dtype, float scale, void* cuda_stream,
+                           int32_t* device_status_or_null, float softcap, void* scratch_or_null,
+                           long long scratch_bytes) {
+  if (softcap < 0.f || softcap != softcap) return OMNI_ERR_SOFTCAP;
+  if (scratch_or_null != nullptr && scratch_bytes < OMNI_ATTN_SCRATCH_BYTES) return OMNI_ERR_SCRATCH;
+  return omni::forward(false, q, k, v, o, lse_or_null, kv_num_blocks, kv_indices, block_mask_types,
+                       partial_idx_or_null, partial_bool_or_null, partial_bits_or_null, B, H,
+                       seqlen_padded, seqlen_orig, head_dim, q_block, kv_block, max_blocks, num_partial,
+                       dtype, scale, cuda_stream, device_status_or_null, scratch_or_null, softcap);
 }
 
 int omni_attn_fwd_simple_sm100(const void* q, const void* k, const void* v, void* o,
@@ -314,6 +333,7 @@ const char* omni_attn_error_string(int code) {
     case OMNI_ERR_CUDA: return "a CUDA call failed (see omni_attn_last_cuda_error)";
     case OMNI_ERR_NO_DRIVER_ENTRY: return "cuTensorMapEncodeTiled not available from the CUDA driver";
     case OMNI_ERR_SCRATCH: return "scratch buffer smaller than OMNI_ATTN_SCRATCH_BYTES";
+    case OMNI_ERR_SOFTCAP: return "softcap must be >= 0 (0 = none); the plain kernel has no soft-cap";
     case OMNI_ERR_NOALLOC_LIMIT:
       return "byte-per-element partial pool has more than OMNI_ATTN_NOALLOC_MAX_PARTIAL (1024) tiles: too large for "
              "the built-in scratch; pass a bit-packed pool or use omni_attn_fwd_scratch_sm100";

@@ -50,6 +50,8 @@ struct FwdParams {
   float scale;           // softmax scale
   float scale_log2;      // scale * log2(e)
   float inv_scale_log2;  // 1 / scale_log2
+  float cap_in;          // soft-cap: scale / softcap (0 = no soft-cap)
+  float cap_out;         // soft-cap: softcap / scale
   int group_heads;       // heads per scheduling group of the warp-specialised kernel (>= 1)
   int num_units;         // work units of the warp-specialised kernel: ceil(nq / 2) * BH
   int o_aligned32;       // output base address is 32-byte aligned (256-bit stores allowed)
@@ -188,6 +190,23 @@ __device__ __forceinline__ void apply_allow(const uint32_t (&allow)[4], float (&
 #pragma unroll
   for (int j = 0; j < 128; ++j) {
     s[j] = ((allow[j >> 5] >> (j & 31)) & 1u) ? s[j] : -INFINITY;
+  }
+}
+
+// Tanh soft-cap of the Transfusion attention (transfusion_pytorch/transfusion.py:298-299, :358-364,
+// :967): scaled score -> softcap * tanh(scaled score / softcap), applied before masking. The raw
+// score s is replaced by the raw score that gives the capped value, (softcap / scale) * tanh(s *
+// scale / softcap), so everything downstream is unchanged. tanh(y) = 1 - 2 / (exp(2y) + 1) with
+// ex2.approx and rcp.approx (absolute error around 1e-7; tanh.approx would be 2^-11 relative, too
+// coarse for a log-sum-exp tolerance of 1e-3 once multiplied by the cap).
+__device__ __forceinline__ void soft_cap_scores(float (&s)[128], float cap_in, float cap_out) {
+  const float k = cap_in * 2.8853900817779268f;  // 2 * log2(e)
+#pragma unroll
+  for (int j = 0; j < 128; ++j) {
+    const float t = ex2_approx(s[j] * k);
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t + 1.f));
+    s[j] = cap_out * fmaf(-2.f, r, 1.f);
   }
 }
 

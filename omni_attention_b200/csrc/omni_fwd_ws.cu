@@ -118,7 +118,7 @@ __device__ __forceinline__ void decode_unit(const FwdParams& p, int unit, int np
   bh = grp * G + rem % heads_here;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool SOFTCAP>
 __global__ void __launch_bounds__(kWsThreads, 1)
 omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -243,7 +243,7 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after();
         if (cnt == 0) { OMNI_USTAMP(2); }
 
-        if constexpr (Cfg::kTwoPass) {
+        if constexpr (Cfg::kTwoPass && !SOFTCAP) {
         // pass 1: row maximum over the whole row (the scores are dropped again right away)
         float mx;
         {
@@ -267,8 +267,10 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         st.l = st.l * alpha + sum;
         } else {
+        // one pass with the whole row in registers (with a soft-cap the capped scores are worth keeping)
         float s[128];
         load_scores(tS, s);
+        if constexpr (SOFTCAP) soft_cap_scores(s, p.cap_in, p.cap_out);
         if (masked) apply_allow(allow, s);
         const float alpha = softmax_update(st, row_max(s), p.scale_log2, kLazyRescaleLog2);
         if (cnt > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) rescale_o<D>(tO, alpha);
@@ -630,11 +632,11 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool SOFTCAP>
 static cudaError_t launch_ws_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
                                FwdParams p, cudaStream_t stream) {
   using Cfg = WsCfg<D>;
-  auto kern = omni_fwd_ws_kernel<D, BF16>;
+  auto kern = omni_fwd_ws_kernel<D, BF16, SOFTCAP>;
   static bool attr_done[64] = {};
   cudaError_t e = ensure_smem_attr(kern, Cfg::kSmemBytes, attr_done);
   if (e != cudaSuccess) return e;
@@ -672,12 +674,21 @@ static cudaError_t launch_ws_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, c
 
 cudaError_t launch_ws(int head_dim, bool bf16, const CUtensorMap& tmQ, const CUtensorMap& tmK,
                       const CUtensorMap& tmV, const FwdParams& p, cudaStream_t stream) {
+  const bool cap = p.cap_out != 0.f;
   if (head_dim == 64) {
-    return bf16 ? launch_ws_t<64, true>(tmQ, tmK, tmV, p, stream)
-                : launch_ws_t<64, false>(tmQ, tmK, tmV, p, stream);
+    if (cap) {
+      return bf16 ? launch_ws_t<64, true, true>(tmQ, tmK, tmV, p, stream)
+                  : launch_ws_t<64, false, true>(tmQ, tmK, tmV, p, stream);
+    }
+    return bf16 ? launch_ws_t<64, true, false>(tmQ, tmK, tmV, p, stream)
+                : launch_ws_t<64, false, false>(tmQ, tmK, tmV, p, stream);
   }
-  return bf16 ? launch_ws_t<128, true>(tmQ, tmK, tmV, p, stream)
-              : launch_ws_t<128, false>(tmQ, tmK, tmV, p, stream);
+  if (cap) {
+    return bf16 ? launch_ws_t<128, true, true>(tmQ, tmK, tmV, p, stream)
+                : launch_ws_t<128, false, true>(tmQ, tmK, tmV, p, stream);
+  }
+  return bf16 ? launch_ws_t<128, true, false>(tmQ, tmK, tmV, p, stream)
+              : launch_ws_t<128, false, false>(tmQ, tmK, tmV, p, stream);
 }
 
 }  // namespace omni

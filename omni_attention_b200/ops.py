@@ -31,6 +31,7 @@ _lib = None
 ABI_SYMBOLS = (
     "omni_attn_fwd_sm100",
     "omni_attn_fwd_scratch_sm100",
+    "omni_attn_fwd_ex_sm100",
     "omni_attn_fwd_noalloc_sm100",
     "omni_attn_fwd_simple_sm100",
     "omni_attn_pack_partial_masks_sm100",
@@ -69,6 +70,8 @@ def load_library() -> ctypes.CDLL:
         fn.restype = i32
     lib.omni_attn_fwd_scratch_sm100.argtypes = fwd_args + [vp, ctypes.c_longlong]
     lib.omni_attn_fwd_scratch_sm100.restype = i32
+    lib.omni_attn_fwd_ex_sm100.argtypes = fwd_args + [f32, vp, ctypes.c_longlong]
+    lib.omni_attn_fwd_ex_sm100.restype = i32
     lib.omni_attn_pack_partial_masks_sm100.argtypes = [vp, vp, i32, vp]
     lib.omni_attn_pack_partial_masks_sm100.restype = i32
     lib.omni_attn_build_mask_sm100.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp,
@@ -174,7 +177,8 @@ def _device_mask(bm: OmniBlockMask, device: torch.device, pack_bits: bool) -> di
 
 def omni_attention_forward_out(q: Tensor, k: Tensor, v: Tensor, out: Tensor, block_mask: OmniBlockMask,
                                seqlen_orig: int, scale: Optional[float] = None, lse: Optional[Tensor] = None,
-                               status: Optional[Tensor] = None, kernel: str = "ws", pack_bits: bool = True) -> None:
+                               status: Optional[Tensor] = None, kernel: str = "ws", pack_bits: bool = True,
+                               softcap: Optional[float] = None) -> None:
     """Launch the forward on padded, contiguous CUDA tensors; writes ``out`` (and ``lse``) in place."""
     if not (q.is_cuda and k.is_cuda and v.is_cuda and out.is_cuda):
         raise OmniAttnError("omni_attention needs CUDA tensors (there is no CPU path)")
@@ -207,7 +211,12 @@ def omni_attention_forward_out(q: Tensor, k: Tensor, v: Tensor, out: Tensor, blo
                 B, H, N, int(seqlen_orig), D, block_mask.Q_BLOCK_SIZE, block_mask.KV_BLOCK_SIZE,
                 int(m["idx"].shape[3]), m["num_partial"], 1 if q.dtype == torch.bfloat16 else 0,
                 float(scale) if scale is not None else 0.0, stream, _ptr(status))
-        if kernel == "ws":
+        if softcap is not None and softcap > 0:
+            if kernel == "simple":
+                raise OmniAttnError("the plain kernel has no soft-cap")
+            sc = _scratch_for(q.device, stream) if kernel == "ws" else None
+            rc = lib.omni_attn_fwd_ex_sm100(*args, float(softcap), _ptr(sc), SCRATCH_BYTES if sc is not None else 0)
+        elif kernel == "ws":
             # dynamic unit hand-out: one small scratch buffer per (device, stream), reused by every
             # call on that stream (calls on one stream never overlap)
             rc = lib.omni_attn_fwd_scratch_sm100(*args, _scratch_for(q.device, stream).data_ptr(), SCRATCH_BYTES)
@@ -240,12 +249,13 @@ def _pad_to_block(x: Tensor, block: int) -> Tuple[Tensor, int]:
 
 def omni_attention(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMask,
                    scale: Optional[float] = None, return_lse: bool = False, kernel: str = "ws",
-                   check_status: bool = False) -> Union[Tensor, Tuple[Tensor, Tensor]]:
+                   check_status: bool = False, softcap: Optional[float] = None) -> Union[Tensor, Tuple[Tensor, Tensor]]:
     """Block-mask attention forward on a B200.
 
     query/key/value: [B, H, N, D] fp16 or bf16 CUDA tensors with Q_len == KV_len, D in {64, 128};
     ``block_mask`` built for the length padded to 128. Returns ``out[:, :, :N]`` (and
-    ``lse[:, :, :N]``, natural log, when ``return_lse``). ``check_status=True`` synchronises and
+    ``lse[:, :, :N]``, natural log, when ``return_lse``). ``softcap`` > 0 applies the Transfusion attention's
+    tanh soft-cap to the scaled scores before masking (transfusion_pytorch/transfusion.py:358-364). ``check_status=True`` synchronises and
     raises if the kernel reported a bounded-wait timeout or an out-of-range block index.
     """
     B, H, Q, D = query.shape
@@ -265,7 +275,7 @@ def omni_attention(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBl
     out = torch.empty_like(qp)
     lse = torch.empty(B, H, qp.shape[2], dtype=torch.float32, device=qp.device) if return_lse else None
     status = torch.zeros(1, dtype=torch.int32, device=qp.device) if check_status else None
-    omni_attention_forward_out(qp, kp, vp, out, block_mask, n_orig, scale, lse, status, kernel)
+    omni_attention_forward_out(qp, kp, vp, out, block_mask, n_orig, scale, lse, status, kernel, softcap=softcap)
     if check_status:
         code = int(status.item())
         if code & 0xFF == STATUS_WAIT_TIMEOUT:

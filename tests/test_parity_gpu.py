@@ -352,3 +352,31 @@ def test_gpu_mask_builder_at_c5_size(cuda_device):
     torch.cuda.synchronize()
     out_bytes = 4 * (3 * cpu.kv_indices.numel() + cpu.kv_num_blocks.numel())
     print(f"C5 mask build (incl. host sync and bit expansion): {e0.elapsed_time(e1) / 5:.3f} ms, index tensors {out_bytes / 1e6:.0f} MB")
+
+
+@pytest.mark.parametrize("D,dtype", [(64, torch.float16), (128, torch.bfloat16)])
+def test_transfusion_attention_core_with_softcap(cuda_device, D, dtype):
+    """The Transfusion attention slot: GPU-built modality mask + tanh soft-cap (value 50 as in the
+    model, and a small cap that really bends the scores) against the oracle's restatement of the
+    model's non-flex branch (transfusion_pytorch/transfusion.py:963-983)."""
+    from omni_attention_b200.transfusion import transfusion_attention_core, transfusion_block_mask
+
+    g = torch.Generator().manual_seed(D)
+    B, H, N = 2, 2, 1024
+    mp = _random_modality_positions(B, N, g)
+    q, k, v = (torch.randn(B, H, N, D, generator=g).to(dtype) for _ in range(3))
+    q = q * 3.0   # large scores so that the cap matters
+    bm = transfusion_block_mask(mp.to(cuda_device), H, N)
+    dense = orc.naive_attn_mask(N, mp.long())
+    for cap in (50.0, 4.0):
+        out = transfusion_attention_core(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), bm, softcap_value=cap)
+        ref, ref_lse = orc.attention_dense_mask(q.float(), k.float(), v.float(), orc.to_score_mask(dense).unsqueeze(1),
+                                                softcap=cap)
+        assert_parity(out, None, ref, None, f"softcap {cap} D={D}")
+        _, lse = omni_attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), bm, return_lse=True, softcap=cap)
+        assert float((lse.cpu() - ref_lse).abs().max()) <= LSE_ATOL
+    # the cap must change the result on this input (otherwise the test proves nothing)
+    plain = omni_attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), bm)
+    assert float((plain.float() - out.float()).abs().max()) > 0.05
+    with pytest.raises(ops.OmniAttnError):
+        omni_attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), bm, kernel="simple", softcap=4.0)
