@@ -51,6 +51,7 @@ extern "C" {
 #define OMNI_ERR_NO_DRIVER_ENTRY (-11) /* cuTensorMapEncodeTiled is not available from the driver */
 #define OMNI_ERR_SCRATCH (-12)         /* scratch buffer smaller than OMNI_ATTN_SCRATCH_BYTES */
 #define OMNI_ERR_SOFTCAP (-14)         /* softcap negative or NaN */
+#define OMNI_ERR_WORKSPACE (-15)       /* omni_attn_bwd_sm100: workspace smaller than omni_attn_bwd_workspace_bytes() */
 #define OMNI_ERR_NOALLOC_LIMIT (-13)   /* omni_attn_fwd_noalloc_sm100: byte mask pool larger than the built-in scratch holds */
 
 /* Values a kernel can leave in *device_status (0 = clean run). Low byte = kind, upper bits = the
@@ -208,6 +209,35 @@ int omni_attn_build_mask_sm100(const int32_t* modality_positions, int B, int M, 
                                int32_t* block_mask_types, int32_t* partial_idx, uint32_t* partial_bits,
                                uint8_t* partial_bool_or_null, int partial_capacity, int32_t* num_partial_out,
                                void* scratch, long long scratch_bytes, void* cuda_stream);
+
+/* Backward pass: dQ, dK, dV from the gradient of the output, with the block lists of the forward
+ * pass and the log-sum-exp it saved.
+ *
+ * No counterpart in the reference, which is forward-only (omni-attn-mma/pybind/omni_attn.cc:70-77
+ * exports no gradient function, and omni-attn-mma/omni_attn_torch.py wraps the forward in no
+ * autograd.Function). What is differentiated is the reference's forward definition
+ * softmax((Q K^T) * scale + mask) V (omni-attn-mma/omni_attn_torch.py:348-387) with the mask semantics of
+ * omni_attn_fwd_sm100; a row that attended nothing gets zero gradient.
+ *
+ *  q, k, v, o, d_o     in  [B, H, seqlen_padded, head_dim] 16-bit; o and lse are the results of the
+ *                      forward call on the same q, k, v, lists and scale. Rows of q and d_o at positions
+ *                      >= seqlen_orig take no part but must hold finite values.
+ *  lse                 in  [B, H, seqlen_padded] fp32, natural log
+ *  dq, dk, dv          out [B, H, seqlen_padded, head_dim], same 16-bit type; rows >= seqlen_orig are zero
+ *  workspace           device memory, at least omni_attn_bwd_workspace_bytes(B, H, seqlen_padded) bytes,
+ *                      16-byte aligned; holds no state between calls, and two calls that overlap in time
+ *                      need two workspaces
+ * The list, pool, size, dtype, scale, stream and status arguments are those of omni_attn_fwd_sm100.
+ * Three kernels are enqueued on cuda_stream; the result is deterministic (no atomics). */
+long long omni_attn_bwd_workspace_bytes(int B, int H, int seqlen_padded);
+int omni_attn_bwd_sm100(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                        const void* d_o, void* dq, void* dk, void* dv, const int32_t* kv_num_blocks,
+                        const int32_t* kv_indices, const int32_t* block_mask_types,
+                        const int32_t* partial_idx_or_null, const uint8_t* partial_bool_or_null,
+                        const uint32_t* partial_bits_or_null, int B, int H, int seqlen_padded, int seqlen_orig,
+                        int head_dim, int q_block, int kv_block, int max_blocks, int num_partial, int dtype,
+                        float scale, void* cuda_stream, int32_t* device_status_or_null, void* workspace,
+                        long long workspace_bytes);
 
 /* Text for an OMNI_ERR_* code; the pointer is static storage. */
 const char* omni_attn_error_string(int code);

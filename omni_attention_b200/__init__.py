@@ -1,8 +1,10 @@
-"""omni_attention_b200: block-mask ("omni") attention forward for NVIDIA B200 (sm_100a).
+"""omni_attention_b200: block-mask ("omni") attention for NVIDIA B200 (sm_100a), forward and backward.
 
 Public surface (mirrors the reference's operator module omni-attn-mma/omni_attn_torch.py):
   BlockMaskType, OmniBlockMask, build_partial_block_data, create_causal_omni_block_mask  - mask metadata
   omni_attention(q, k, v, block_mask, scale=None, return_lse=False)                        - the operator
+  omni_attention_autograd(q, k, v, block_mask, scale=None)   - the same, differentiable (backward kernels;
+                                                               the reference has no backward)
   install_reference_module()  - makes the `omni_attn` extension module (the reference's five pybind entry
                                 points) importable, so the reference's own wrappers run on these kernels
 """
@@ -10,13 +12,15 @@ from .block_mask import (BlockMaskType, OmniBlockMask, block_mask_from_dense, bl
                          build_partial_block_data, create_causal_omni_block_mask,
                          create_omni_block_mask_from_modality_positions, dense_mask_from_blocks,
                          row_limits_from_modality_positions)
-from .ops import OmniAttnError, omni_attention, omni_attention_forward_out, pack_partial_masks
+from .ops import (OmniAttnError, omni_attention, omni_attention_autograd, omni_attention_backward_out,
+                  omni_attention_forward_out, pack_partial_masks)
 
 __all__ = [
     "BlockMaskType", "OmniBlockMask", "block_mask_from_dense", "block_mask_from_row_limits",
     "build_partial_block_data", "create_causal_omni_block_mask", "create_omni_block_mask_from_modality_positions",
     "dense_mask_from_blocks",
     "row_limits_from_modality_positions", "OmniAttnError", "omni_attention", "omni_attention_forward_out",
+    "omni_attention_autograd", "omni_attention_backward_out",
     "pack_partial_masks", "install_reference_module",
 ]
 

@@ -23,7 +23,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
 ]
-CUDA_SOURCES = ["omni_abi.cu", "omni_fwd_simple.cu", "omni_fwd_ws.cu", "omni_mask_build.cu"]
+CUDA_SOURCES = ["omni_abi.cu", "omni_fwd_simple.cu", "omni_fwd_ws.cu", "omni_mask_build.cu", "omni_bwd.cu"]
 CUDA_HEADERS = ["ptx_sm100.cuh", "omni_common.cuh", "omni_launch.h", os.path.join("..", "..", "include", "omni_attn_sm100.h")]
 
 

@@ -149,6 +149,97 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
   return OMNI_OK;
 }
 
+long long bwd_workspace_bytes(long long BH, int seqlen_padded) {
+  const long long nq = seqlen_padded / kBlock;
+  const long long codes = ((BH * nq * nq * 4 + 255) / 256) * 256;
+  return codes + BH * seqlen_padded * 4;
+}
+
+int backward(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+             void* dq, void* dk, void* dv, const int32_t* kv_num_blocks, const int32_t* kv_indices,
+             const int32_t* types, const int32_t* partial_idx, const uint8_t* partial_bool,
+             const uint32_t* partial_bits, int B, int H, int seqlen_padded, int seqlen_orig, int head_dim,
+             int q_block, int kv_block, int max_blocks, int num_partial, int dtype, float scale, void* stream,
+             int32_t* status, void* workspace, long long workspace_bytes) {
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || lse == nullptr || d_o == nullptr ||
+      dq == nullptr || dk == nullptr || dv == nullptr || kv_num_blocks == nullptr || kv_indices == nullptr ||
+      types == nullptr || workspace == nullptr) {
+    return OMNI_ERR_NULL_POINTER;
+  }
+  if (dtype != OMNI_DTYPE_F16 && dtype != OMNI_DTYPE_BF16) return OMNI_ERR_DTYPE;
+  if (head_dim != 64 && head_dim != 128) return OMNI_ERR_HEAD_DIM;
+  if (q_block != kBlock || kv_block != kBlock) return OMNI_ERR_BLOCK_SIZE;
+  if (seqlen_padded <= 0 || seqlen_padded % kBlock != 0 || seqlen_orig <= 0 || seqlen_orig > seqlen_padded) {
+    return OMNI_ERR_SEQLEN;
+  }
+  if (B <= 0 || H <= 0 || max_blocks <= 0) return OMNI_ERR_SHAPE;
+  const long long BH = static_cast<long long>(B) * H;
+  const long long rows = BH * seqlen_padded;
+  if (rows >= (1LL << 31) || BH > 65535) return OMNI_ERR_SHAPE;
+  if (num_partial < 0) return OMNI_ERR_PARTIAL;
+  if (num_partial > 0 && partial_bool == nullptr && partial_bits == nullptr) return OMNI_ERR_PARTIAL;
+  const int nq = seqlen_padded / kBlock;
+  if (nq > kMaxKvBlocks) return OMNI_ERR_TOO_LONG;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(d_o) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv) || !aligned16(partial_bool) || !aligned16(partial_bits) ||
+      !aligned16(workspace)) {
+    return OMNI_ERR_ALIGNMENT;
+  }
+  if (workspace_bytes < bwd_workspace_bytes(BH, seqlen_padded)) return OMNI_ERR_WORKSPACE;
+
+  const bool bf16 = dtype == OMNI_DTYPE_BF16;
+  CUtensorMap tmQ, tmK, tmV, tmdO;
+  int rc = make_tile_map(&tmQ, q, rows, head_dim, bf16);
+  if (rc != OMNI_OK) return rc;
+  rc = make_tile_map(&tmK, k, rows, head_dim, bf16);
+  if (rc != OMNI_OK) return rc;
+  rc = make_tile_map(&tmV, v, rows, head_dim, bf16);
+  if (rc != OMNI_OK) return rc;
+  rc = make_tile_map(&tmdO, d_o, rows, head_dim, bf16);
+  if (rc != OMNI_OK) return rc;
+
+  BwdParams p;
+  p.f.o = nullptr;
+  p.f.lse = nullptr;
+  p.f.kv_num_blocks = kv_num_blocks;
+  p.f.kv_indices = kv_indices;
+  p.f.types = types;
+  p.f.partial_idx = num_partial > 0 ? partial_idx : nullptr;
+  p.f.partial_bool = num_partial > 0 ? partial_bool : nullptr;
+  p.f.partial_bits = num_partial > 0 ? partial_bits : nullptr;
+  p.f.status = status;
+  p.f.unit_counter = nullptr;
+  p.f.BH = static_cast<int>(BH);
+  p.f.N = seqlen_padded;
+  p.f.seqlen_orig = seqlen_orig;
+  p.f.nq = nq;
+  p.f.max_blocks = max_blocks;
+  p.f.num_partial = num_partial;
+  p.f.scale = scale > 0.f ? scale : 1.f / std::sqrt(static_cast<float>(head_dim));
+  p.f.scale_log2 = p.f.scale * 1.4426950408889634f;
+  p.f.inv_scale_log2 = 1.f / p.f.scale_log2;
+  p.f.cap_in = 0.f;
+  p.f.cap_out = 0.f;
+  p.f.group_heads = 1;
+  p.f.num_units = 0;
+  p.f.o_aligned32 = 0;
+  p.o = o;
+  p.d_o = d_o;
+  p.lse = lse;
+  p.dq = dq;
+  p.dk = dk;
+  p.dv = dv;
+  p.codes = static_cast<uint32_t*>(workspace);
+  p.delta = reinterpret_cast<float*>(static_cast<char*>(workspace) +
+                                     ((BH * nq * nq * 4 + 255) / 256) * 256);
+  cudaError_t e = launch_bwd(head_dim, bf16, tmQ, tmK, tmV, tmdO, p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(e);
+    return OMNI_ERR_CUDA;
+  }
+  return OMNI_OK;
+}
+
 // One thread per output word: 32 mask bytes -> 32 bits.
 __global__ void pack_partial_kernel(const uint8_t* __restrict__ src, uint32_t* __restrict__ dst,
                                     long long n_words) {
@@ -318,6 +409,25 @@ int omni_attn_fwd_noalloc_sm100(const void* q, const void* k, const void* v, voi
                        device_status_or_null, scratch);
 }
 
+long long omni_attn_bwd_workspace_bytes(int B, int H, int seqlen_padded) {
+  if (B <= 0 || H <= 0 || seqlen_padded <= 0 || seqlen_padded % omni::kBlock != 0) return 0;
+  return omni::bwd_workspace_bytes(static_cast<long long>(B) * H, seqlen_padded);
+}
+
+int omni_attn_bwd_sm100(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                        const void* d_o, void* dq, void* dk, void* dv, const int32_t* kv_num_blocks,
+                        const int32_t* kv_indices, const int32_t* block_mask_types,
+                        const int32_t* partial_idx_or_null, const uint8_t* partial_bool_or_null,
+                        const uint32_t* partial_bits_or_null, int B, int H, int seqlen_padded, int seqlen_orig,
+                        int head_dim, int q_block, int kv_block, int max_blocks, int num_partial, int dtype,
+                        float scale, void* cuda_stream, int32_t* device_status_or_null, void* workspace,
+                        long long workspace_bytes) {
+  return omni::backward(q, k, v, o, lse, d_o, dq, dk, dv, kv_num_blocks, kv_indices, block_mask_types,
+                        partial_idx_or_null, partial_bool_or_null, partial_bits_or_null, B, H, seqlen_padded,
+                        seqlen_orig, head_dim, q_block, kv_block, max_blocks, num_partial, dtype, scale,
+                        cuda_stream, device_status_or_null, workspace, workspace_bytes);
+}
+
 const char* omni_attn_error_string(int code) {
   switch (code) {
     case OMNI_OK: return "ok";
@@ -334,6 +444,7 @@ const char* omni_attn_error_string(int code) {
     case OMNI_ERR_NO_DRIVER_ENTRY: return "cuTensorMapEncodeTiled not available from the CUDA driver";
     case OMNI_ERR_SCRATCH: return "scratch buffer smaller than OMNI_ATTN_SCRATCH_BYTES";
     case OMNI_ERR_SOFTCAP: return "softcap must be >= 0 (0 = none); the plain kernel has no soft-cap";
+    case OMNI_ERR_WORKSPACE: return "workspace smaller than omni_attn_bwd_workspace_bytes()";
     case OMNI_ERR_NOALLOC_LIMIT:
       return "byte-per-element partial pool has more than OMNI_ATTN_NOALLOC_MAX_PARTIAL (1024) tiles: too large for "
              "the built-in scratch; pass a bit-packed pool or use omni_attn_fwd_scratch_sm100";

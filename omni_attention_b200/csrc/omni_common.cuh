@@ -57,6 +57,21 @@ struct FwdParams {
   int o_aligned32;       // output base address is 32-byte aligned (256-bit stores allowed)
 };
 
+// Launch parameters of the backward kernels. `f` carries the block lists, the partial-mask pools,
+// the sizes and the softmax scale exactly as the forward pass got them (its o / lse / unit_counter
+// members are not used).
+struct BwdParams {
+  FwdParams f;
+  const void* o;       // [BH, N, D] forward output
+  const void* d_o;     // [BH, N, D] gradient of the output
+  const float* lse;    // [BH, N] log-sum-exp saved by the forward pass (natural log)
+  void* dq;            // [BH, N, D] results, same 16-bit type as the inputs
+  void* dk;
+  void* dv;
+  uint32_t* codes;     // workspace: [BH, nq, nq] resolved entry code of every (Q block, KV block), 0 = not visited
+  float* delta;        // workspace: [BH, N] rowsum(dO * O)
+};
+
 // Resolve entry `i` of the list of (bh, qb). Returns 0 when the entry is not visited.
 __device__ __forceinline__ uint32_t resolve_entry(const FwdParams& p, long long list_base, int i,
                                                   int qb, int& kvb_out) {

@@ -17,6 +17,11 @@ cudaError_t launch_simple(int head_dim, bool bf16, const CUtensorMap& tmQ, const
 cudaError_t launch_ws(int head_dim, bool bf16, const CUtensorMap& tmQ, const CUtensorMap& tmK,
                       const CUtensorMap& tmV, const FwdParams& p, cudaStream_t stream);
 
+// Backward pass: fills the workspace (entry codes, delta), then dK/dV (one CTA per KV block) and dQ
+// (one CTA per Q block).
+cudaError_t launch_bwd(int head_dim, bool bf16, const CUtensorMap& tmQ, const CUtensorMap& tmK,
+                       const CUtensorMap& tmV, const CUtensorMap& tmdO, const BwdParams& p, cudaStream_t stream);
+
 // Sets a kernel's dynamic shared memory limit once per device.
 template <typename K>
 inline cudaError_t ensure_smem_attr(K kern, int bytes, bool (&done)[64]) {

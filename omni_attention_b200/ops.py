@@ -36,6 +36,8 @@ ABI_SYMBOLS = (
     "omni_attn_fwd_simple_sm100",
     "omni_attn_pack_partial_masks_sm100",
     "omni_attn_build_mask_sm100",
+    "omni_attn_bwd_workspace_bytes",
+    "omni_attn_bwd_sm100",
     "omni_attn_error_string",
     "omni_attn_last_cuda_error",
     "omni_attn_abi_version",
@@ -77,6 +79,10 @@ def load_library() -> ctypes.CDLL:
     lib.omni_attn_build_mask_sm100.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp,
                                                ctypes.c_longlong, vp]
     lib.omni_attn_build_mask_sm100.restype = i32
+    lib.omni_attn_bwd_workspace_bytes.argtypes = [i32, i32, i32]
+    lib.omni_attn_bwd_workspace_bytes.restype = ctypes.c_longlong
+    lib.omni_attn_bwd_sm100.argtypes = [vp] * 15 + [i32] * 10 + [f32, vp, vp, vp, ctypes.c_longlong]
+    lib.omni_attn_bwd_sm100.restype = i32
     lib.omni_attn_error_string.argtypes = [i32]
     lib.omni_attn_error_string.restype = ctypes.c_char_p
     lib.omni_attn_last_cuda_error.argtypes = []
@@ -286,6 +292,86 @@ def omni_attention(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBl
     if return_lse:
         return out, lse[:, :, :n_orig]
     return out
+
+
+def omni_attention_backward_out(q: Tensor, k: Tensor, v: Tensor, out: Tensor, lse: Tensor, d_out: Tensor,
+                                dq: Tensor, dk: Tensor, dv: Tensor, block_mask: OmniBlockMask, seqlen_orig: int,
+                                scale: Optional[float] = None, status: Optional[Tensor] = None,
+                                workspace: Optional[Tensor] = None) -> None:
+    """Launch the backward on padded, contiguous CUDA tensors; writes ``dq``, ``dk``, ``dv`` in place.
+    ``out`` and ``lse`` are what the forward returned for the same inputs, mask and scale. The
+    reference has no backward; this is the gradient of its forward definition."""
+    tensors = (q, k, v, out, d_out, dq, dk, dv)
+    if not all(t.is_cuda for t in tensors) or not lse.is_cuda:
+        raise OmniAttnError("omni_attention backward needs CUDA tensors (there is no CPU path)")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise OmniAttnError(f"unsupported dtype {q.dtype}: fp16 or bf16")
+    for t in tensors:
+        if t.dtype != q.dtype or t.shape != q.shape or not t.is_contiguous():
+            raise OmniAttnError("q, k, v, out, d_out, dq, dk, dv must be contiguous and share dtype and shape")
+    B, H, N, D = q.shape
+    if lse.dtype != torch.float32 or lse.numel() != B * H * N or not lse.is_contiguous():
+        raise OmniAttnError("lse must be contiguous float32 [B, H, N]")
+    m = _device_mask(block_mask, q.device, True)
+    lib = load_library()
+    need = int(lib.omni_attn_bwd_workspace_bytes(B, H, N))
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.omni_attn_bwd_sm100(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), d_out.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), m["nb"].data_ptr(), m["idx"].data_ptr(),
+            m["typ"].data_ptr(), _ptr(m["pidx"]), _ptr(m["pbool"]), _ptr(m["pbits"]), B, H, N, int(seqlen_orig), D,
+            block_mask.Q_BLOCK_SIZE, block_mask.KV_BLOCK_SIZE, int(m["idx"].shape[3]), m["num_partial"],
+            1 if q.dtype == torch.bfloat16 else 0, float(scale) if scale is not None else 0.0, stream,
+            _ptr(status), workspace.data_ptr(), workspace.numel() * workspace.element_size())
+    _check(rc)
+
+
+class _OmniAttentionFn(torch.autograd.Function):
+    """Forward and backward kernels as one differentiable op on padded tensors."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, block_mask, seqlen_orig, scale):
+        out = torch.empty_like(q)
+        lse = torch.empty(q.shape[0], q.shape[1], q.shape[2], dtype=torch.float32, device=q.device)
+        omni_attention_forward_out(q, k, v, out, block_mask, seqlen_orig, scale, lse)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.block_mask, ctx.seqlen_orig, ctx.scale = block_mask, seqlen_orig, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, out, lse = ctx.saved_tensors
+        d_out = d_out.contiguous()
+        if ctx.seqlen_orig < q.shape[2]:
+            d_out = d_out.clone()
+            d_out[:, :, ctx.seqlen_orig:] = 0   # padded rows take no part but must be finite
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        omni_attention_backward_out(q, k, v, out, lse, d_out, dq, dk, dv, ctx.block_mask, ctx.seqlen_orig, ctx.scale)
+        return dq, dk, dv, None, None, None
+
+
+def omni_attention_autograd(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMask,
+                            scale: Optional[float] = None) -> Tensor:
+    """``omni_attention`` for training: same inputs and output, differentiable with respect to
+    query, key and value (the gradients come from omni_attn_bwd_sm100)."""
+    B, H, Q, D = query.shape
+    if key.shape != (B, H, Q, D) or value.shape != (B, H, Q, D):
+        raise OmniAttnError(f"key/value shape must equal query shape {(B, H, Q, D)} (Q_len == KV_len)")
+    if D not in (64, 128):
+        raise ValueError(f"Unsupported head_dim={D}. Built for sm_100a: 64, 128.")
+    if block_mask.Q_BLOCK_SIZE != 128 or block_mask.KV_BLOCK_SIZE != 128:
+        raise ValueError("Unsupported block size: Q_BLOCK_SIZE and KV_BLOCK_SIZE must be 128.")
+    qp, n_orig = _pad_to_block(query, 128)
+    kp, _ = _pad_to_block(key, 128)
+    vp, _ = _pad_to_block(value, 128)
+    if qp.shape[2] != block_mask.q_len or kp.shape[2] != block_mask.kv_len:
+        raise OmniAttnError(
+            f"padded length {qp.shape[2]} does not match the mask's q_len/kv_len ({block_mask.q_len}/{block_mask.kv_len})")
+    out = _OmniAttentionFn.apply(qp.contiguous(), kp.contiguous(), vp.contiguous(), block_mask, n_orig, scale)
+    return out[:, :, :n_orig]
 
 
 def default_scale(head_dim: int) -> float:
