@@ -110,3 +110,20 @@ def test_oracle_against_reference_in_process():
     o16, _ = orc.attention_dense_mask(q.bfloat16(), k.bfloat16(), v.bfloat16(), ref.to_score_mask(rbm))
     r16 = ref.naive_attention_with_dense_mask(q.bfloat16(), k.bfloat16(), v.bfloat16(), mask=ref.to_score_mask(rbm))
     assert torch.equal(o16, r16)
+
+
+def test_oracle_gradient_matches_torch_sdpa_autograd():
+    """The oracle's backward is autograd through its own forward; cross-check it on a causal mask
+    with the gradient of torch's scaled_dot_product_attention."""
+    import torch.nn.functional as F
+    from omni_attention_b200 import create_causal_omni_block_mask
+    from oracle import omni_oracle as orc
+
+    torch.manual_seed(0)
+    q, k, v, d_out = (torch.randn(1, 2, 256, 64) for _ in range(4))
+    bm = create_causal_omni_block_mask(1, 2, 256, 256)
+    dq, dk, dv = orc.block_mask_attention_backward(q, k, v, bm, d_out)
+    qs, ks, vs = (t.clone().requires_grad_(True) for t in (q, k, v))
+    F.scaled_dot_product_attention(qs, ks, vs, is_causal=True).backward(d_out)
+    for a, b in ((dq, qs.grad), (dk, ks.grad), (dv, vs.grad)):
+        assert float((a - b).abs().max()) < 2e-5
