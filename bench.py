@@ -189,7 +189,7 @@ def run_reference(args, rank, world):
 def run_ours(args, rank, local_rank, world):
     import torch.distributed as dist
 
-    from omni_attention_b200.ops import omni_attention, omni_attention_forward_out
+    from omni_attention_b200.ops import load_library, omni_attention, omni_attention_forward_out
 
     cfg = inputs.CONFIGS[args.workload]
     dev = torch.device("cuda", local_rank)
@@ -265,14 +265,34 @@ def run_ours(args, rank, local_rank, world):
         c5 = {"ms": ms5, "flops_all_ranks": fl5}
         del q5, k5, v5, o5
 
+    # ---- backward pass on the same workload (three launches per step), reported aside ---------------
+    bwd_ms = 0.0
+    if not args.no_backward:
+        from omni_attention_b200.ops import omni_attention_backward_out
+
+        lse = torch.empty(1, cfg.H, cfg.N, dtype=torch.float32, device=dev)
+        omni_attention_forward_out(q, k, v, out, bm, cfg.N, None, lse, status, "ws")
+        d_out = (torch.randn(q.shape, device=dev, generator=torch.Generator(device=dev).manual_seed(77 + rank)) * 0.5).to(q.dtype)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+        wsp = torch.empty(int(load_library().omni_attn_bwd_workspace_bytes(1, cfg.H, cfg.N)), dtype=torch.uint8, device=dev)
+
+        def bstep():
+            omni_attention_backward_out(q, k, v, out, lse, d_out, dq, dk, dv, bm, cfg.N, None, status, wsp)
+
+        bstep()
+        if world > 1:
+            dist.barrier()
+        bwd_ms = time_steps(bstep, 10, 3, flush) / 10
+        del d_out, dq, dk, dv, wsp
+
     # ---- reduce over ranks (MAX of time, SUM of work) ---------------------------------------------
-    vals = torch.tensor([total_ms, e2e_ms, c5["ms"] if c5 else 0.0, float(flops)], dtype=torch.float64, device=dev)
+    vals = torch.tensor([total_ms, e2e_ms, c5["ms"] if c5 else 0.0, float(flops), bwd_ms], dtype=torch.float64, device=dev)
     if world > 1:
         mx = vals.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = vals.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        total_ms, e2e_ms, c5ms, flops_all = float(mx[0]), float(mx[1]), float(mx[2]), float(sm[3])
+        total_ms, e2e_ms, c5ms, flops_all, bwd_ms = float(mx[0]), float(mx[1]), float(mx[2]), float(sm[3]), float(mx[4])
     else:
         c5ms, flops_all = float(vals[2]), float(flops)
     if rank != 0:
@@ -305,6 +325,14 @@ def run_ours(args, rank, local_rank, world):
     if c5 is not None:
         line["c5_sharded"] = {"workload": "C5: B=4 H=32 N=32768 D=128 bf16, 128 (batch,head) pairs split over the ranks (strong scaling)",
                               "fwd_ms": c5ms, "value": c5["flops_all_ranks"] / (c5ms * 1e-3) / 1e12, "unit": UNIT, "steps": 5}
+    if bwd_ms > 0:
+        # five tile contractions per visited block (S, dP, dV, dK, dQ) = 2.5 x the forward count; the
+        # kernels execute seven (S and dP are recomputed by the dQ kernel)
+        bwd_tf = 2.5 * flops / (bwd_ms * 1e-3) / 1e12
+        line["backward"] = {"ms": bwd_ms, "value": 2.5 * flops_all / (bwd_ms * 1e-3) / 1e12, "unit": UNIT, "steps": 10,
+                            "launches_per_step": 3, "flop_count": "10*128*128*D per visited block",
+                            "roofline_frac": bwd_tf / peak_tf,
+                            "kernels": "omni_bwd_prep_kernel, omni_bwd_dkdv_kernel, omni_bwd_dq_kernel"}
     if world == 1 and not args.no_cpu_baseline:
         torch.set_num_threads(os.cpu_count() or 1)
         line["cpu_baseline"] = cpu_baseline(cfg, bm)
@@ -320,6 +348,7 @@ def main():
     ap.add_argument("--workload", default="C4", choices=["C3", "C4"])
     ap.add_argument("--no-c5", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-backward", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 

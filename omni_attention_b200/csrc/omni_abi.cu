@@ -220,7 +220,8 @@ int backward(const void* q, const void* k, const void* v, const void* o, const f
   p.f.inv_scale_log2 = 1.f / p.f.scale_log2;
   p.f.cap_in = 0.f;
   p.f.cap_out = 0.f;
-  p.f.group_heads = 1;
+  // Q, K, V and dO of a head group share L2: half as many heads per group as in the forward pass
+  p.f.group_heads = group_heads_for(BH, seqlen_padded, head_dim) / 2 > 0 ? group_heads_for(BH, seqlen_padded, head_dim) / 2 : 1;
   p.f.num_units = 0;
   p.f.o_aligned32 = 0;
   p.o = o;

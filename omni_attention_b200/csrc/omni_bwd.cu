@@ -21,8 +21,12 @@
 //                             visited K, V stream; dQ += dS K with dS from TMEM.
 // S and dP are recomputed in both kernels (7 tile contractions per visited tile instead of 5), which
 // buys a deterministic result with no atomics and no fp32 dQ buffer.
-// Both kernels are plain (one 128-thread CTA, thread = TMEM lane = one row, thread 0 issues TMA and
-// tcgen05.mma); loads are overlapped with compute, MMAs and the per-element work alternate.
+// Both kernels are plain: one CTA of 8 compute warps plus one warp whose first lane issues TMA and
+// tcgen05.mma (a lane that issues MMAs must not share its warp with lanes that spin on a barrier);
+// a tile row (= TMEM lane) is shared by two compute threads, one per warpgroup, each taking 64 of
+// its 128 columns. Loads are overlapped with compute; MMAs and the per-element work alternate.
+#include <type_traits>
+
 #include "omni_common.cuh"
 #include "omni_launch.h"
 
@@ -36,8 +40,13 @@ struct BwdCfg {
   static constexpr int kTmemCols = 512;
   static constexpr int kVecBytes = 2 * 2 * kBlock * 4;   // LSE and delta of a Q block, two stages
   static constexpr int kBitsBytes = kBlock * 16;          // one bit-packed partial tile
-  static constexpr int kSmemBytes = 6 * kTileBytes + kVecBytes + kBitsBytes + 256 + 1024;
+  static constexpr int kListBytes = kMaxKvBlocks * 4 + kMaxKvBlocks * 2 + 16;   // codes, visit list, its length
+  static constexpr int kSmemBytes = 6 * kTileBytes + kVecBytes + kBitsBytes + kListBytes + 256 + 1024;
 };
+
+constexpr int kBwdComputeThreads = 256;
+constexpr int kBwdThreads = kBwdComputeThreads + 32;
+constexpr int kBwdIssuer = kBwdComputeThreads;   // thread that issues TMA and MMAs
 
 template <bool BF16>
 __device__ __forceinline__ float2 unpack2(uint32_t w) {
@@ -123,14 +132,14 @@ __device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uin
   }
 }
 
-// One accumulator row out of TMEM, times `mul`, as 16-bit values to global memory (zeros when
-// `have_acc` is false).
-template <int D, bool BF16>
+// One accumulator row (32-column chunks [kFirstChunk, kEndChunk) of it) out of TMEM, times `mul`, as
+// 16-bit values to global memory (zeros when `have_acc` is false).
+template <int D, bool BF16, int kFirstChunk = 0, int kEndChunk = D / 32>
 __device__ __forceinline__ void bwd_store_row(uint32_t taddr_row, bool have_acc, float mul, void* base,
                                               long long row_index) {
   uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(base) + row_index * (D * 2));
 #pragma unroll
-  for (int c = 0; c < D / 32; ++c) {
+  for (int c = kFirstChunk; c < kEndChunk; ++c) {
     uint32_t r[32];
     if (have_acc) {
       tmem_ld32(taddr_row + 32 * c, r);
@@ -149,6 +158,43 @@ __device__ __forceinline__ void bwd_store_row(uint32_t taddr_row, bool have_acc,
   }
 }
 
+// One row or column of the entry-code table -> shared memory, plus the ascending list of the blocks
+// it visits (walking the table in global memory instead costs one dependent load per skipped
+// block). Every thread of the CTA must call it.
+__device__ __forceinline__ int bwd_build_visit_list(const uint32_t* src, long long stride, int n, uint32_t* code_s,
+                                                    uint16_t* vis_s, int* n_vis_s) {
+  for (int i = threadIdx.x; i < n; i += blockDim.x) code_s[i] = __ldg(src + i * stride);
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int count = 0;
+    for (int base = 0; base < n; base += 32) {
+      const bool on = base + lane < n && code_s[base + lane] != 0u;
+      const uint32_t any = __ballot_sync(0xFFFFFFFFu, on);
+      if (on) vis_s[count + __popc(any & ((1u << lane) - 1u))] = static_cast<uint16_t>(base + lane);
+      count += __popc(any);
+    }
+    if (lane == 0) *n_vis_s = count;
+  }
+  __syncthreads();
+  return *n_vis_s;
+}
+
+// CTA index -> (block, batch*head) for the two tile kernels. Heads are taken in groups of
+// `group_heads` (sized on the host so that a group's Q, K, V and dO stay in L2 together); inside a
+// group the blocks run from the longest lists to the shortest for causal-like masks (`descending`:
+// from the last block to the first) with the group's heads adjacent, so that the long CTAs of every
+// head start early and the grid drains with short ones.
+__device__ __forceinline__ void bwd_decode_cta(const FwdParams& f, int cta, bool descending, int& block, int& bh) {
+  const int G = f.group_heads;
+  const int grp = cta / (f.nq * G);
+  const int rem = cta - grp * f.nq * G;
+  const int heads_here = min(G, f.BH - grp * G);
+  const int b = rem / heads_here;
+  block = descending ? f.nq - 1 - b : b;
+  bh = grp * G + rem % heads_here;
+}
+
 // log-sum-exp (natural log) -> subtrahend in the log2 domain; a row that attended nothing
 // (-inf) gives +inf, which turns every probability of the row into exp2(-inf) = 0.
 __device__ __forceinline__ float lse_to_log2(float lse) {
@@ -156,12 +202,13 @@ __device__ __forceinline__ float lse_to_log2(float lse) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// 2. dK, dV. Grid (nq, BH): blockIdx.x = KV block. Thread t owns key row t of the block.
+// 2. dK, dV. One CTA per (KV block, batch*head), see bwd_decode_cta. Threads t and t + 128 own key row t of the block
+// (query columns [0,64) and [64,128)).
 // TMEM: S^T [0,128)  dP^T [128,256)  dV [256,256+D)  dK [384,384+D). P^T (16-bit) is written over
 // the first 64 columns of S^T, dS^T over the first 64 columns of dP^T.
 // ---------------------------------------------------------------------------------------------
 template <int D, bool BF16>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                      const BwdParams p) {
@@ -174,10 +221,13 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t sV = sK + Cfg::kTileBytes;
   const uint32_t sQ = sV + Cfg::kTileBytes;            // two stages
   const uint32_t sdO = sQ + 2 * Cfg::kTileBytes;       // two stages
-  float* lse_s = reinterpret_cast<float*>(smem + 6 * Cfg::kTileBytes);   // [2][128], log2 domain
-  float* delta_s = lse_s + 2 * kBlock;                                    // [2][128]
+  float* lse_s = reinterpret_cast<float*>(smem + 6 * Cfg::kTileBytes);   // [2][128], -LSE in the log2 domain
+  float* delta_s = lse_s + 2 * kBlock;                                    // [2][128], -delta
   uint32_t* bits_s = reinterpret_cast<uint32_t*>(delta_s + 2 * kBlock);   // [128][4]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(bits_s + kBlock * 4);
+  uint32_t* code_s = bits_s + kBlock * 4;                                   // [kMaxKvBlocks]
+  uint16_t* vis_s = reinterpret_cast<uint16_t*>(code_s + kMaxKvBlocks);      // [kMaxKvBlocks]
+  int* n_vis_s = reinterpret_cast<int*>(vis_s + kMaxKvBlocks);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(n_vis_s + 4);
   const uint32_t bar_kv = smem_u32(bars + 0);
   const uint32_t bar_ld = smem_u32(bars + 1);   // [2]
   const uint32_t bar_s = smem_u32(bars + 3);
@@ -187,9 +237,12 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
-  const int kvb = blockIdx.x;
-  const int bh = blockIdx.y;
+  const bool compute = tid < kBwdComputeThreads;
+  const int half = (tid >> 7) & 1;  // which 64 query columns of the tile this thread works on
+  const int t = tid & 127;          // key row of the tile = TMEM lane
   const int nq = p.f.nq;
+  int kvb, bh;
+  bwd_decode_cta(p.f, static_cast<int>(blockIdx.x), false, kvb, bh);
 
   if (tid == 0) {
     mbar_init(bar_kv, 1);
@@ -213,7 +266,7 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   tc_fence_after();
 
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   const uint32_t tSt = tmem_base;
   const uint32_t tdPt = tmem_base + 128;
   const uint32_t tdV = tmem_base + 256;
@@ -224,37 +277,39 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const long long row0 = static_cast<long long>(bh) * p.f.N;
   // column kvb of this head's code table: which Q blocks visit this KV block, and how
-  const uint32_t* col = p.codes + static_cast<long long>(bh) * nq * nq + kvb;
-  auto next_visited = [&](int from, uint32_t& code) -> int {
-    int qb = from;
-    code = 0u;
-    while (qb < nq) {
-      code = __ldg(col + static_cast<long long>(qb) * nq);
-      if (code != 0u) break;
-      ++qb;
+  const int n_vis = bwd_build_visit_list(p.codes + static_cast<long long>(bh) * nq * nq + kvb, nq, nq, code_s, vis_s,
+                                         n_vis_s);
+  auto visited_at = [&](int i, uint32_t& code) -> int {
+    if (i >= n_vis) {
+      code = 0u;
+      return nq;
     }
+    const int qb = vis_s[i];
+    code = code_s[qb];
     return qb;
   };
   // Stage a Q block: TMA for Q and dO (thread 0), LSE and delta by every thread for its own row.
   auto stage_q_block = [&](int qb, int stage) {
-    if (tid == 0) {
+    if (tid == kBwdIssuer) {
       const uint32_t bar = bar_ld + 8 * stage;
       mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
       const int y = static_cast<int>(row0 + qb * kBlock);
       bwd_load_tile<D>(sQ + stage * Cfg::kTileBytes, &tmQ, bar, y);
       bwd_load_tile<D>(sdO + stage * Cfg::kTileBytes, &tmdO, bar, y);
     }
-    const int q_abs = qb * kBlock + tid;
-    const long long row = row0 + q_abs;
-    const bool live = q_abs < p.f.seqlen_orig;
-    lse_s[stage * kBlock + tid] = live ? lse_to_log2(__ldg(p.lse + row)) : INFINITY;
-    delta_s[stage * kBlock + tid] = live ? __ldg(p.delta + row) : 0.f;
+    if (tid < kBlock) {
+      const int q_abs = qb * kBlock + tid;
+      const long long row = row0 + q_abs;
+      const bool live = q_abs < p.f.seqlen_orig;
+      lse_s[stage * kBlock + tid] = live ? -lse_to_log2(__ldg(p.lse + row)) : -INFINITY;   // negated
+      delta_s[stage * kBlock + tid] = live ? -__ldg(p.delta + row) : 0.f;                   // negated
+    }
   };
 
   uint32_t code_cur = 0u, code_next = 0u;
-  int qb_cur = next_visited(0, code_cur);
+  int qb_cur = visited_at(0, code_cur);
   if (qb_cur < nq) {
-    if (tid == 0) {
+    if (tid == kBwdIssuer) {
       mbar_expect_tx(bar_kv, 2 * Cfg::kTileBytes);
       const int y = static_cast<int>(row0 + kvb * kBlock);
       bwd_load_tile<D>(sK, &tmK, bar_kv, y);
@@ -263,103 +318,169 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     stage_q_block(qb_cur, 0);
   }
   __syncthreads();   // the first block's LSE / delta vectors are read by every thread
-  const int k_abs = kvb * kBlock + tid;
+  const int k_abs = kvb * kBlock + t;
   const bool key_live = k_abs < p.f.seqlen_orig;
 
+#ifdef OMNI_BWD_PROFILE
+  long long acc_t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long t_prev = clock64();
+#define OMNI_BSTAMP(i) if (tid == 0 || tid == kBwdIssuer) { const long long t_now = clock64(); acc_t[i] += t_now - t_prev; t_prev = t_now; }
+#else
+#define OMNI_BSTAMP(i)
+#endif
   int it = 0;
   while (qb_cur < nq) {
+    OMNI_BSTAMP(0);
     const int stage = it & 1;
     const uint32_t ph = static_cast<uint32_t>(it & 1);
-    // the other stage was last read by the MMAs of the previous iteration, which have completed
-    const int qb_next = next_visited(qb_cur + 1, code_next);
-    if (qb_next < nq) stage_q_block(qb_next, stage ^ 1);
-
-    if (tid == 0) {
+    if (tid == kBwdIssuer) {
       if (it == 0) mbar_wait(bar_kv, 0, abort_flag, p.f.status, 50);
       mbar_wait(bar_ld + 8 * stage, static_cast<uint32_t>((it >> 1) & 1), abort_flag, p.f.status, 51);
       tc_fence_after();
+      OMNI_BSTAMP(3);
       bwd_mma_ss<D>(tSt, sK, sQ + stage * Cfg::kTileBytes, idesc_ss);     // S^T  = K Q^T
       bwd_mma_ss<D>(tdPt, sV, sdO + stage * Cfg::kTileBytes, idesc_ss);   // dP^T = V dO^T
       tc_commit(bar_s);
+      OMNI_BSTAMP(1);
     }
+    // Stage the next Q block while the MMAs run. The other stage was last read by the MMAs of the
+    // previous iteration, which have completed.
+    const int qb_next = visited_at(it + 1, code_next);
+    if (qb_next < nq) stage_q_block(qb_next, stage ^ 1);
 
-    // Allow-bits of this thread's key over the 128 query rows of the block (bit r = query row r).
+    // Allow-bits of this thread's key over its 64 query rows of the block (bit r of word w = query
+    // row 64 * half + 32 * w + r).
     const uint32_t type = code_cur & kCodeTypeMask;
-    uint32_t allow[4] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
+    uint32_t allow[2] = {0xFFFFFFFFu, 0xFFFFFFFFu};
     if (type == kTypePartial) {   // uniform over the CTA
-      uint32_t rowbits[4];
-      load_partial_row(p.f, code_cur >> 3, tid, rowbits);   // row tid of the tile = query row tid
-      *reinterpret_cast<uint4*>(bits_s + 4 * tid) = make_uint4(rowbits[0], rowbits[1], rowbits[2], rowbits[3]);
+      if (tid < kBlock) {
+        uint32_t rowbits[4];
+        load_partial_row(p.f, code_cur >> 3, tid, rowbits);   // row tid of the tile = query row tid
+        *reinterpret_cast<uint4*>(bits_s + 4 * tid) = make_uint4(rowbits[0], rowbits[1], rowbits[2], rowbits[3]);
+      }
       __syncthreads();
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < 2; ++w) {
         uint32_t acc = 0u;
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
-          acc |= ((bits_s[4 * (32 * w + r) + (tid >> 5)] >> (tid & 31)) & 1u) << r;
+          acc |= ((bits_s[4 * (64 * half + 32 * w + r) + (t >> 5)] >> (t & 31)) & 1u) << r;
         }
         allow[w] = acc;
       }
     } else if (type == kTypeCausal) {
       // diagonal block: key t is seen by query rows r >= t
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const int d = tid - 32 * w;   // lowest allowed bit in this word
+      for (int w = 0; w < 2; ++w) {
+        const int d = t - 64 * half - 32 * w;   // lowest allowed bit in this word
         allow[w] = d <= 0 ? 0xFFFFFFFFu : (d > 31 ? 0u : ~((1u << d) - 1u));
       }
     }
-    if (!key_live) allow[0] = allow[1] = allow[2] = allow[3] = 0u;
-    const int q_live = p.f.seqlen_orig - qb_cur * kBlock;   // query rows [0, q_live) exist
-    if (q_live < kBlock) clip_row(q_live, allow);
-
-    mbar_wait(bar_s, ph, abort_flag, p.f.status, 52);
-    tc_fence_after();
-
-    const float* lse_c = lse_s + stage * kBlock;
-    const float* del_c = delta_s + stage * kBlock;
+    if (!key_live) allow[0] = allow[1] = 0u;
+    const bool masked = type != kTypeFull || (code_cur & kCodeClip) || (qb_cur + 1) * kBlock > p.f.seqlen_orig;
+    const int q_live = p.f.seqlen_orig - qb_cur * kBlock - 64 * half;   // query rows [0, q_live) of this half exist
+    if (q_live < 64) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t rs[32], rd[32];
-      tmem_ld32(tSt + lane_base + 32 * c, rs);
-      tmem_ld32(tdPt + lane_base + 32 * c, rd);
-      tc_wait_ld();
-      uint32_t pp[16], dd[16];
-      const uint32_t aw = allow[c];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float2 l2 = *reinterpret_cast<const float2*>(lse_c + 32 * c + 2 * j);
-        const float2 dl = *reinterpret_cast<const float2*>(del_c + 32 * c + 2 * j);
-        const bool ok0 = (aw >> (2 * j)) & 1u, ok1 = (aw >> (2 * j + 1)) & 1u;
-        const float p0 = ok0 ? ex2_approx(fmaf(__uint_as_float(rs[2 * j]), p.f.scale_log2, -l2.x)) : 0.f;
-        const float p1 = ok1 ? ex2_approx(fmaf(__uint_as_float(rs[2 * j + 1]), p.f.scale_log2, -l2.y)) : 0.f;
-        const float d0 = ok0 ? p0 * (__uint_as_float(rd[2 * j]) - dl.x) : 0.f;
-        const float d1 = ok1 ? p1 * (__uint_as_float(rd[2 * j + 1]) - dl.y) : 0.f;
-        pp[j] = pack2<BF16>(p0, p1);
-        dd[j] = pack2<BF16>(d0, d1);
+      for (int w = 0; w < 2; ++w) {
+        const int d = q_live - 1 - 32 * w;
+        allow[w] &= d >= 31 ? 0xFFFFFFFFu : (d < 0 ? 0u : ((2u << d) - 1u));
       }
-      tmem_st16(tSt + lane_base + 16 * c, pp);
-      tmem_st16(tdPt + lane_base + 16 * c, dd);
     }
-    tc_wait_st();
+
+    uint32_t pp[2][16], dd[2][16];
+    OMNI_BSTAMP(2);
+    if (compute) {
+    mbar_wait_warp(bar_s, ph, abort_flag, p.f.status, 52);
+    tc_fence_after();
+    OMNI_BSTAMP(3);
+    const float* lse_c = lse_s + stage * kBlock + 64 * half;
+    const float* del_c = delta_s + stage * kBlock + 64 * half;
+    const float2 c2 = make_float2(p.f.scale_log2, p.f.scale_log2);
+    // two copies of the loop, so that tiles without any masking (the bulk) carry no select at all
+    auto tile_math = [&](auto masked_c) {
+      constexpr bool kMasked = decltype(masked_c)::value;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tSt + lane_base + 64 * half + 32 * c, rs);
+        tmem_ld32(tdPt + lane_base + 64 * half + 32 * c, rd);
+        tc_wait_ld();
+        const uint32_t aw = allow[c];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 nl = *reinterpret_cast<const float2*>(lse_c + 32 * c + 2 * j);
+          const float2 nd = *reinterpret_cast<const float2*>(del_c + 32 * c + 2 * j);
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), c2, nl);
+          float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+          float2 ds = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd));
+          if constexpr (kMasked) {
+            const bool ok0 = (aw >> (2 * j)) & 1u, ok1 = (aw >> (2 * j + 1)) & 1u;
+            pr.x = ok0 ? pr.x : 0.f;
+            pr.y = ok1 ? pr.y : 0.f;
+            ds.x = ok0 ? ds.x : 0.f;
+            ds.y = ok1 ? ds.y : 0.f;
+          }
+          pp[c][j] = pack2<BF16>(pr.x, pr.y);
+          dd[c][j] = pack2<BF16>(ds.x, ds.y);
+        }
+      }
+    };
+    if (masked) {   // uniform over the CTA
+      tile_math(std::true_type{});
+    } else {
+      tile_math(std::false_type{});
+    }
+    }
+    OMNI_BSTAMP(4);
+    // The packed P^T / dS^T rows land on columns [0,64) of S^T / dP^T, which the other warpgroup may
+    // still be reading: everybody reads first, then everybody writes.
     tc_fence_before();
     __syncthreads();
+    tc_fence_after();
+    if (compute) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tmem_st16(tSt + lane_base + 32 * half + 16 * c, pp[c]);
+        tmem_st16(tdPt + lane_base + 32 * half + 16 * c, dd[c]);
+      }
+      tc_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();
+    OMNI_BSTAMP(5);
 
-    if (tid == 0) {
+    if (tid == kBwdIssuer) {
       tc_fence_after();
       bwd_mma_ts<D>(tdV, tSt, sdO + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dV += P^T dO
       bwd_mma_ts<D>(tdK, tdPt, sQ + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dK += dS^T Q
       tc_commit(bar_acc);
     }
-    mbar_wait(bar_acc, ph, abort_flag, p.f.status, 53);
+    OMNI_BSTAMP(6);
+    if (compute) {
+      mbar_wait_warp(bar_acc, ph, abort_flag, p.f.status, 53);
+    } else if (tid == kBwdIssuer) {
+      mbar_wait(bar_acc, ph, abort_flag, p.f.status, 53);
+    }
     tc_fence_after();
+    OMNI_BSTAMP(7);
     qb_cur = qb_next;
     code_cur = code_next;
     ++it;
   }
 
+#ifdef OMNI_BWD_PROFILE
+  if ((tid == 0 || tid == kBwdIssuer) && p.f.status != nullptr) {
+    unsigned long long* prof = reinterpret_cast<unsigned long long*>(p.f.status + 4) + (tid == 0 ? 0 : 10);
+    for (int i = 0; i < 8; ++i) atomicAdd(prof + i, static_cast<unsigned long long>(acc_t[i]));
+    atomicAdd(prof + 8, static_cast<unsigned long long>(it));
+  }
+#endif
   const long long out_row = row0 + k_abs;
-  bwd_store_row<D, BF16>(tdV + lane_base, it > 0, 1.f, p.dv, out_row);
-  bwd_store_row<D, BF16>(tdK + lane_base, it > 0, p.f.scale, p.dk, out_row);
+  if (compute && half == 0) {
+    bwd_store_row<D, BF16>(tdV + lane_base, it > 0, 1.f, p.dv, out_row);
+  } else if (compute) {
+    bwd_store_row<D, BF16>(tdK + lane_base, it > 0, p.f.scale, p.dk, out_row);
+  }
 
   tc_fence_before();
   __syncthreads();
@@ -367,12 +488,13 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 }
 
 // ---------------------------------------------------------------------------------------------
-// 3. dQ. Grid (nq, BH): blockIdx.x = Q block. Thread t owns query row t of the block.
+// 3. dQ. One CTA per (Q block, batch*head), see bwd_decode_cta. Threads t and t + 128 own query row t of the block
+// (key columns [0,64) and [64,128)).
 // TMEM: S [0,128)  dP [128,256)  dQ [256,256+D). dS (16-bit) is written over the first 64 columns
 // of dP.
 // ---------------------------------------------------------------------------------------------
 template <int D, bool BF16>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const BwdParams p) {
@@ -385,7 +507,10 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t sdO = sQ + Cfg::kTileBytes;
   const uint32_t sK = sdO + Cfg::kTileBytes;           // two stages
   const uint32_t sV = sK + 2 * Cfg::kTileBytes;        // two stages
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * Cfg::kTileBytes);
+  uint32_t* code_s = reinterpret_cast<uint32_t*>(smem + 6 * Cfg::kTileBytes);   // [kMaxKvBlocks]
+  uint16_t* vis_s = reinterpret_cast<uint16_t*>(code_s + kMaxKvBlocks);          // [kMaxKvBlocks]
+  int* n_vis_s = reinterpret_cast<int*>(vis_s + kMaxKvBlocks);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(n_vis_s + 4);
   const uint32_t bar_q = smem_u32(bars + 0);
   const uint32_t bar_ld = smem_u32(bars + 1);   // [2]
   const uint32_t bar_s = smem_u32(bars + 3);
@@ -395,9 +520,12 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
-  const int qb = blockIdx.x;
-  const int bh = blockIdx.y;
+  const bool compute = tid < kBwdComputeThreads;
+  const int half = (tid >> 7) & 1;  // which 64 key columns of the tile this thread works on
+  const int t = tid & 127;          // query row of the tile = TMEM lane
   const int nq = p.f.nq;
+  int qb, bh;
+  bwd_decode_cta(p.f, static_cast<int>(blockIdx.x), true, qb, bh);
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
@@ -421,7 +549,7 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after();
 
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   const uint32_t tS = tmem_base;
   const uint32_t tdP = tmem_base + 128;
   const uint32_t tdQ = tmem_base + 256;
@@ -430,19 +558,20 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   constexpr uint32_t idesc_ts = umma_idesc_f16(128, D, fmt, 1);
 
   const long long row0 = static_cast<long long>(bh) * p.f.N;
-  const uint32_t* codes = p.codes + (static_cast<long long>(bh) * nq + qb) * nq;   // row qb of the table
-  auto next_visited = [&](int from, uint32_t& code) -> int {
-    int kvb = from;
-    code = 0u;
-    while (kvb < nq) {
-      code = __ldg(codes + kvb);
-      if (code != 0u) break;
-      ++kvb;
+  // row qb of this head's code table: the KV blocks this Q block visits, and how
+  const int n_vis = bwd_build_visit_list(p.codes + (static_cast<long long>(bh) * nq + qb) * nq, 1, nq, code_s, vis_s,
+                                         n_vis_s);
+  auto visited_at = [&](int i, uint32_t& code) -> int {
+    if (i >= n_vis) {
+      code = 0u;
+      return nq;
     }
+    const int kvb = vis_s[i];
+    code = code_s[kvb];
     return kvb;
   };
   auto stage_kv_block = [&](int kvb, int stage) {
-    if (tid == 0) {
+    if (tid == kBwdIssuer) {
       const uint32_t bar = bar_ld + 8 * stage;
       mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
       const int y = static_cast<int>(row0 + kvb * kBlock);
@@ -451,16 +580,20 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   };
 
-  const int q_abs = qb * kBlock + tid;
+  const int q_abs = qb * kBlock + t;
   const long long my_row = row0 + q_abs;
   const bool q_live = q_abs < p.f.seqlen_orig;
-  const float lse2 = q_live ? lse_to_log2(__ldg(p.lse + my_row)) : INFINITY;
-  const float delta = q_live ? __ldg(p.delta + my_row) : 0.f;
+  // a row beyond the sequence (or one that attended nothing) gets -LSE = -inf: every probability 0
+  const float neg_lse2 = q_live ? -lse_to_log2(__ldg(p.lse + my_row)) : -INFINITY;
+  const float neg_delta = q_live ? -__ldg(p.delta + my_row) : 0.f;
+  const float2 c2 = make_float2(p.f.scale_log2, p.f.scale_log2);
+  const float2 nl2 = make_float2(neg_lse2, neg_lse2);
+  const float2 nd2 = make_float2(neg_delta, neg_delta);
 
   uint32_t code_cur = 0u, code_next = 0u;
-  int kvb_cur = next_visited(0, code_cur);
+  int kvb_cur = visited_at(0, code_cur);
   if (kvb_cur < nq) {
-    if (tid == 0) {
+    if (tid == kBwdIssuer) {
       mbar_expect_tx(bar_q, 2 * Cfg::kTileBytes);
       const int y = static_cast<int>(row0 + qb * kBlock);
       bwd_load_tile<D>(sQ, &tmQ, bar_q, y);
@@ -473,10 +606,7 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   while (kvb_cur < nq) {
     const int stage = it & 1;
     const uint32_t ph = static_cast<uint32_t>(it & 1);
-    const int kvb_next = next_visited(kvb_cur + 1, code_next);
-    if (kvb_next < nq) stage_kv_block(kvb_next, stage ^ 1);
-
-    if (tid == 0) {
+    if (tid == kBwdIssuer) {
       if (it == 0) mbar_wait(bar_q, 0, abort_flag, p.f.status, 60);
       mbar_wait(bar_ld + 8 * stage, static_cast<uint32_t>((it >> 1) & 1), abort_flag, p.f.status, 61);
       tc_fence_after();
@@ -484,50 +614,79 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       bwd_mma_ss<D>(tdP, sdO, sV + stage * Cfg::kTileBytes, idesc_ss);   // dP = dO V^T
       tc_commit(bar_s);
     }
+    // stage the next KV block while the MMAs run
+    const int kvb_next = visited_at(it + 1, code_next);
+    if (kvb_next < nq) stage_kv_block(kvb_next, stage ^ 1);
 
     const bool masked = (code_cur & kCodeTypeMask) != kTypeFull || (code_cur & kCodeClip);
     uint32_t allow[4] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
-    if (masked) build_allow(p.f, code_cur, kvb_cur, tid, allow);
+    if (masked) build_allow(p.f, code_cur, kvb_cur, t, allow);
 
-    mbar_wait(bar_s, ph, abort_flag, p.f.status, 62);
+    uint32_t dd[2][16];
+    if (compute) {
+    mbar_wait_warp(bar_s, ph, abort_flag, p.f.status, 62);
     tc_fence_after();
-
+    auto tile_math = [&](auto masked_c) {
+      constexpr bool kMasked = decltype(masked_c)::value;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t rs[32], rd[32];
-      tmem_ld32(tS + lane_base + 32 * c, rs);
-      tmem_ld32(tdP + lane_base + 32 * c, rd);
-      tc_wait_ld();
-      uint32_t dd[16];
-      const uint32_t aw = allow[c];
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tS + lane_base + 64 * half + 32 * c, rs);
+        tmem_ld32(tdP + lane_base + 64 * half + 32 * c, rd);
+        tc_wait_ld();
+        const uint32_t aw = allow[2 * half + c];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const bool ok0 = (aw >> (2 * j)) & 1u, ok1 = (aw >> (2 * j + 1)) & 1u;
-        const float p0 = ex2_approx(fmaf(__uint_as_float(rs[2 * j]), p.f.scale_log2, -lse2));
-        const float p1 = ex2_approx(fmaf(__uint_as_float(rs[2 * j + 1]), p.f.scale_log2, -lse2));
-        const float d0 = (ok0 && q_live) ? p0 * (__uint_as_float(rd[2 * j]) - delta) : 0.f;
-        const float d1 = (ok1 && q_live) ? p1 * (__uint_as_float(rd[2 * j + 1]) - delta) : 0.f;
-        dd[j] = pack2<BF16>(d0, d1);
+        for (int j = 0; j < 16; ++j) {
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), c2, nl2);
+          const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+          float2 ds = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd2));
+          if constexpr (kMasked) {
+            ds.x = ((aw >> (2 * j)) & 1u) ? ds.x : 0.f;
+            ds.y = ((aw >> (2 * j + 1)) & 1u) ? ds.y : 0.f;
+          }
+          dd[c][j] = pack2<BF16>(ds.x, ds.y);
+        }
       }
-      tmem_st16(tdP + lane_base + 16 * c, dd);
+    };
+    if (masked) {   // uniform over the CTA
+      tile_math(std::true_type{});
+    } else {
+      tile_math(std::false_type{});
     }
-    tc_wait_st();
+    }
+    // dS lands on columns [0,64) of dP, which the other warpgroup may still be reading
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (compute) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) tmem_st16(tdP + lane_base + 32 * half + 16 * c, dd[c]);
+      tc_wait_st();
+    }
     tc_fence_before();
     __syncthreads();
 
-    if (tid == 0) {
+    if (tid == kBwdIssuer) {
       tc_fence_after();
       bwd_mma_ts<D>(tdQ, tdP, sK + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dQ += dS K
       tc_commit(bar_acc);
     }
-    mbar_wait(bar_acc, ph, abort_flag, p.f.status, 63);
+    if (compute) {
+      mbar_wait_warp(bar_acc, ph, abort_flag, p.f.status, 63);
+    } else if (tid == kBwdIssuer) {
+      mbar_wait(bar_acc, ph, abort_flag, p.f.status, 63);
+    }
     tc_fence_after();
     kvb_cur = kvb_next;
     code_cur = code_next;
     ++it;
   }
 
-  bwd_store_row<D, BF16>(tdQ + lane_base, it > 0, p.f.scale, p.dq, my_row);
+  if (compute && half == 0) {
+    bwd_store_row<D, BF16, 0, D / 64>(tdQ + lane_base, it > 0, p.f.scale, p.dq, my_row);
+  } else if (compute) {
+    bwd_store_row<D, BF16, D / 64, D / 32>(tdQ + lane_base, it > 0, p.f.scale, p.dq, my_row);
+  }
 
   tc_fence_before();
   __syncthreads();
@@ -550,10 +709,11 @@ static cudaError_t launch_bwd_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, 
   omni_bwd_prep_kernel<D, BF16><<<grid, 128, 0, stream>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  dkdv<<<grid, 128, Cfg::kSmemBytes, stream>>>(tmQ, tmK, tmV, tmdO, p);
+  const unsigned ctas = static_cast<unsigned>(p.f.nq) * static_cast<unsigned>(p.f.BH);
+  dkdv<<<ctas, kBwdThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmK, tmV, tmdO, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  dq<<<grid, 128, Cfg::kSmemBytes, stream>>>(tmQ, tmK, tmV, tmdO, p);
+  dq<<<ctas, kBwdThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmK, tmV, tmdO, p);
   return cudaGetLastError();
 }
 
