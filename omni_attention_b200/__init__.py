@@ -11,6 +11,7 @@ Public surface (mirrors the reference's operator module omni-attn-mma/omni_attn_
 from .block_mask import (BlockMaskType, OmniBlockMask, block_mask_from_dense, block_mask_from_row_limits,
                          build_partial_block_data, create_causal_omni_block_mask,
                          create_omni_block_mask_from_modality_positions, dense_mask_from_blocks,
+                         omni_block_mask_from_flex_block_mask, retile_block_mask,
                          row_limits_from_modality_positions)
 from .ops import (OmniAttnError, omni_attention, omni_attention_autograd, omni_attention_backward_out,
                   omni_attention_forward_out, pack_partial_masks)
@@ -18,7 +19,7 @@ from .ops import (OmniAttnError, omni_attention, omni_attention_autograd, omni_a
 __all__ = [
     "BlockMaskType", "OmniBlockMask", "block_mask_from_dense", "block_mask_from_row_limits",
     "build_partial_block_data", "create_causal_omni_block_mask", "create_omni_block_mask_from_modality_positions",
-    "dense_mask_from_blocks",
+    "dense_mask_from_blocks", "omni_block_mask_from_flex_block_mask", "retile_block_mask",
     "row_limits_from_modality_positions", "OmniAttnError", "omni_attention", "omni_attention_forward_out",
     "omni_attention_autograd", "omni_attention_backward_out",
     "pack_partial_masks", "install_reference_module",

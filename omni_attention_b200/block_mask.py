@@ -396,3 +396,145 @@ def create_omni_block_mask_from_modality_positions(modality_positions: Tensor, b
         return build_block_mask_cuda(modality_positions, batch, nheads, q_len, padded, dev)
     limits, plain = _limits_from_modality_tensor(modality_positions, q_len, padded)
     return block_mask_from_row_limits(limits, nheads, plain, 128, True).to(dev)
+
+
+def _stack_block_masks(parts, B: int, H: int) -> OmniBlockMask:
+    """Join per-(batch, head) single-slice masks (row-major over B*H, equal geometry) into one mask;
+    partial pools are concatenated and the indices shifted."""
+    first = parts[0]
+    nb = torch.cat([p.kv_num_blocks for p in parts], 0).view(B, H, -1)
+    idx = torch.cat([p.kv_indices for p in parts], 0).view(B, H, *first.kv_indices.shape[2:])
+    typ = torch.cat([p.block_mask_types for p in parts], 0).view(B, H, *first.block_mask_types.shape[2:])
+    pools, pidx, base = [], [], 0
+    cache = {}
+    for p in parts:
+        if p.partial_block_masks is None or p.partial_block_masks.shape[0] == 0:
+            pidx.append(torch.full_like(p.kv_indices, -1))
+            continue
+        key = id(p)
+        if key not in cache:            # a slice object shared by several heads brings its tiles once
+            cache[key] = base
+            pools.append(p.partial_block_masks)
+            base += p.partial_block_masks.shape[0]
+        off = cache[key]
+        pi = p.partial_block_mask_indices
+        pidx.append(torch.where(pi >= 0, pi + off, pi))
+    bm = OmniBlockMask(nb.contiguous(), idx.contiguous(), typ.contiguous(), first.q_len, first.kv_len,
+                       first.Q_BLOCK_SIZE, first.KV_BLOCK_SIZE)
+    if pools:
+        bm.partial_block_mask_indices = torch.cat(pidx, 0).view(idx.shape).to(torch.int32).contiguous()
+        bm.partial_block_masks = torch.cat(pools, 0).contiguous()
+    return bm
+
+
+def retile_block_mask(bm: OmniBlockMask, block: int = 128) -> OmniBlockMask:
+    """The same attention pattern on another square block size.
+
+    The reference's launchers accept 64x64 as well as 128x128 blocks
+    (omni-attn-mma/mma/omni_attn_shared_kv.cu:780-888); the sm_100a kernels are built for 128x128
+    only, so a 64-block mask is re-expressed here: each slice is expanded with the semantics of
+    ``dense_mask_from_blocks`` and re-derived with ``block_mask_from_dense`` (a 128x128 tile whose four
+    64x64 quadrants differ becomes PARTIAL). Heads of a batch element that share one pattern are
+    converted once. One [N, N] boolean slice is alive at a time.
+    """
+    B, H = bm.kv_num_blocks.shape[:2]
+    n_pad = -(-max(bm.q_len, bm.kv_len) // block) * block
+    parts, seen = [], {}
+    have_pool = bm.partial_block_mask_indices is not None and bm.partial_block_masks is not None
+    for b in range(B):
+        for h in range(H):
+            fields = [bm.kv_num_blocks[b, h], bm.kv_indices[b, h], bm.block_mask_types[b, h]]
+            if have_pool:
+                fields.append(bm.partial_block_mask_indices[b, h])
+            hit = None
+            for (ob, oh), part in seen.items():
+                if ob == b and all(torch.equal(x, y) for x, y in zip(fields, part[1])):
+                    hit = part[0]
+                    break
+            if hit is None:
+                dense = dense_mask_from_blocks(bm, (b * H + h, b * H + h + 1))[0]
+                full = torch.zeros(n_pad, n_pad, dtype=torch.bool, device=dense.device)
+                full[: dense.shape[0], : dense.shape[1]] = dense
+                hit = block_mask_from_dense(full[None, None], block)
+                seen[(b, h)] = (hit, fields)
+            parts.append(hit)
+    return _stack_block_masks(parts, B, H)
+
+
+def omni_block_mask_from_flex_block_mask(flex_block_mask, materialize_partial: bool = True) -> OmniBlockMask:
+    """OmniBlockMask from a ``torch.nn.attention.flex_attention.BlockMask``
+    (omni-attn-mma/omni_attn_torch.py:226-290).
+
+    ``materialize_partial=False`` is the reference's conversion to the letter: the blocks flex lists
+    as needing ``mask_mod`` (``kv_indices``) become PARTIAL entries without element masks - which the
+    expansion and the kernels read as CAUSAL - and flex's full blocks are dropped, as there.
+    The default also carries over ``full_kv_indices`` as FULL entries and evaluates ``mask_mod`` on
+    every partial block into the element-mask pool, so that the result attends exactly where flex
+    does. Flex masks on another block size come back re-tiled to 128 (``retile_block_mask``).
+    """
+    q_len, kv_len = (int(x) for x in flex_block_mask.seq_lengths)
+    bs = getattr(flex_block_mask, "BLOCK_SIZE", None)
+    Bq = int(getattr(flex_block_mask, "Q_BLOCK_SIZE", bs[0] if bs is not None else 128))
+    Bk = int(getattr(flex_block_mask, "KV_BLOCK_SIZE", bs[1] if bs is not None else 128))
+
+    def lift(t):
+        while t.dim() < 3:
+            t = t.unsqueeze(0)
+        return t
+
+    p_nb = lift(flex_block_mask.kv_num_blocks.clone()).to(torch.int32)
+    p_idx = flex_block_mask.kv_indices.clone()
+    while p_idx.dim() < 4:
+        p_idx = p_idx.unsqueeze(0)
+    p_idx = p_idx.to(torch.int32)
+    B, H, nq = p_nb.shape
+    mb = p_idx.shape[3]
+    dev = p_nb.device
+    slot = torch.arange(mb, device=dev).view(1, 1, 1, mb)
+    if not materialize_partial:
+        typ = torch.where(slot < p_nb.unsqueeze(-1), int(BlockMaskType.PARTIAL), int(BlockMaskType.MASKED)).to(torch.int32)
+        return OmniBlockMask(p_nb, p_idx.contiguous(), typ.contiguous(), q_len, kv_len, Bq, Bk)
+
+    nk = -(-kv_len // Bk)
+    grid = torch.zeros(B, H, nq, nk, dtype=torch.int32, device=dev)
+    b_, h_, q_, i_ = (slot < p_nb.unsqueeze(-1)).nonzero(as_tuple=True)
+    grid[b_, h_, q_, p_idx[b_, h_, q_, i_].long()] = int(BlockMaskType.PARTIAL)
+    f_nb = getattr(flex_block_mask, "full_kv_num_blocks", None)
+    if f_nb is not None:
+        f_nb = lift(f_nb).to(torch.int32)
+        f_idx = flex_block_mask.full_kv_indices
+        while f_idx.dim() < 4:
+            f_idx = f_idx.unsqueeze(0)
+        fslot = torch.arange(f_idx.shape[3], device=dev).view(1, 1, 1, -1)
+        fb, fh, fq, fi = (fslot < f_nb.unsqueeze(-1)).nonzero(as_tuple=True)
+        grid[fb, fh, fq, f_idx[fb, fh, fq, fi].long()] = int(BlockMaskType.FULL)
+    # element masks of the partial blocks, straight from mask_mod
+    pb, ph, pq, pk = (grid == int(BlockMaskType.PARTIAL)).nonzero(as_tuple=True)
+    m = pb.numel()
+    tiles = torch.zeros(m, Bq, Bk, dtype=torch.bool, device=dev)
+    mask_mod = flex_block_mask.mask_mod
+    r = torch.arange(Bq, device=dev).view(Bq, 1)
+    c = torch.arange(Bk, device=dev).view(1, Bk)
+    for j in range(m):
+        qi = pq[j] * Bq + r
+        ki = pk[j] * Bk + c
+        t = mask_mod(pb[j], ph[j], qi, ki)
+        tiles[j] = torch.as_tensor(t, dtype=torch.bool, device=dev).expand(Bq, Bk) & (qi < q_len) & (ki < kv_len)
+    # a partial block that turns out to allow everything is typed FULL, one that allows nothing is dropped
+    allf = tiles.flatten(1).all(1)
+    none = ~tiles.flatten(1).any(1)
+    grid[pb[allf], ph[allf], pq[allf], pk[allf]] = int(BlockMaskType.FULL)
+    grid[pb[none], ph[none], pq[none], pk[none]] = int(BlockMaskType.MASKED)
+    keep = ~(allf | none)
+    nb, idx, typ = _pack_lists(grid)
+    bm = OmniBlockMask(nb, idx, typ, -(-q_len // Bq) * Bq, nk * Bk, Bq, Bk)
+    if bool(keep.any()):
+        number = torch.full((B, H, nq, nk), -1, dtype=torch.int32, device=dev)
+        number[pb[keep], ph[keep], pq[keep], pk[keep]] = torch.arange(int(keep.sum()), dtype=torch.int32, device=dev)
+        pidx = torch.gather(number, -1, idx.long())
+        pidx = torch.where(typ == int(BlockMaskType.PARTIAL), pidx, torch.full_like(pidx, -1))
+        bm.partial_block_mask_indices = pidx.contiguous()
+        bm.partial_block_masks = tiles[keep].contiguous()
+    if Bq != 128 or Bk != 128:
+        bm = retile_block_mask(bm, 128)
+    return bm

@@ -253,31 +253,58 @@ def _pad_to_block(x: Tensor, block: int) -> Tuple[Tensor, int]:
     return torch.nn.functional.pad(x, (0, 0, 0, rem)), n
 
 
-def omni_attention(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMask,
-                   scale: Optional[float] = None, return_lse: bool = False, kernel: str = "ws",
-                   check_status: bool = False, softcap: Optional[float] = None) -> Union[Tensor, Tuple[Tensor, Tensor]]:
-    """Block-mask attention forward on a B200.
-
-    query/key/value: [B, H, N, D] fp16 or bf16 CUDA tensors with Q_len == KV_len, D in {64, 128};
-    ``block_mask`` built for the length padded to 128. Returns ``out[:, :, :N]`` (and
-    ``lse[:, :, :N]``, natural log, when ``return_lse``). ``softcap`` > 0 applies the Transfusion attention's
-    tanh soft-cap to the scaled scores before masking (transfusion_pytorch/transfusion.py:358-364). ``check_status=True`` synchronises and
-    raises if the kernel reported a bounded-wait timeout or an out-of-range block index.
-    """
+def _prepare(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMask, scale: Optional[float]):
+    """Shape checks and the conversions that map everything the reference's launchers accept
+    (omni-attn-mma/mma/omni_attn_shared_kv.cu:725-741: head_dim 32/64/128, blocks 64 or 128) onto what
+    the sm_100a kernels are built for (head_dim 64/128, 128x128 blocks):
+      * the sequence is zero-padded to a multiple of 128 (omni_attn_torch.py:1261-1284);
+      * a 64x64-block mask is re-tiled to 128x128 once and cached on the mask object;
+      * head_dim 32 is zero-padded to 64 with the scale kept at 1/sqrt(32): zero columns change
+        neither Q K^T nor the first 32 output columns.
+    Returns padded contiguous q, k, v, the mask to use, the scale, and the original length / head_dim."""
     B, H, Q, D = query.shape
     if key.shape != (B, H, Q, D) or value.shape != (B, H, Q, D):
         raise OmniAttnError(f"key/value shape must equal query shape {(B, H, Q, D)} (Q_len == KV_len)")
-    if D not in (64, 128):
-        raise ValueError(f"Unsupported head_dim={D}. Built for sm_100a: 64, 128.")
-    if block_mask.Q_BLOCK_SIZE != 128 or block_mask.KV_BLOCK_SIZE != 128:
-        raise ValueError("Unsupported block size: Q_BLOCK_SIZE and KV_BLOCK_SIZE must be 128.")
+    if D not in (32, 64, 128):
+        raise ValueError(f"Unsupported head_dim={D}. Supported: 32, 64, 128.")
+    sizes = (block_mask.Q_BLOCK_SIZE, block_mask.KV_BLOCK_SIZE)
+    if sizes == (64, 64):
+        hit = block_mask._cache.get("retiled128")
+        if hit is None:
+            from .block_mask import retile_block_mask
+
+            hit = retile_block_mask(block_mask, 128)
+            block_mask._cache["retiled128"] = hit
+        block_mask = hit
+    elif sizes != (128, 128):
+        raise ValueError("Unsupported block size: Q_BLOCK_SIZE and KV_BLOCK_SIZE must both be 64 or both be 128.")
+    if D == 32:
+        if scale is None:
+            scale = 1.0 / math.sqrt(32)
+        query, key, value = (torch.nn.functional.pad(t, (0, 32)) for t in (query, key, value))
     qp, n_orig = _pad_to_block(query, 128)
     kp, _ = _pad_to_block(key, 128)
     vp, _ = _pad_to_block(value, 128)
     if qp.shape[2] != block_mask.q_len or kp.shape[2] != block_mask.kv_len:
         raise OmniAttnError(
             f"padded length {qp.shape[2]} does not match the mask's q_len/kv_len ({block_mask.q_len}/{block_mask.kv_len})")
-    qp, kp, vp = qp.contiguous(), kp.contiguous(), vp.contiguous()
+    return qp.contiguous(), kp.contiguous(), vp.contiguous(), block_mask, scale, n_orig, D
+
+
+def omni_attention(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMask,
+                   scale: Optional[float] = None, return_lse: bool = False, kernel: str = "ws",
+                   check_status: bool = False, softcap: Optional[float] = None) -> Union[Tensor, Tuple[Tensor, Tensor]]:
+    """Block-mask attention forward on a B200.
+
+    query/key/value: [B, H, N, D] fp16 or bf16 CUDA tensors with Q_len == KV_len, D in {32, 64, 128}
+    (32 runs zero-padded to 64); ``block_mask`` with 128x128 blocks built for the length padded to 128,
+    or with 64x64 blocks (re-tiled to 128 once). Returns ``out[:, :, :N]`` (and
+    ``lse[:, :, :N]``, natural log, when ``return_lse``). ``softcap`` > 0 applies the Transfusion attention's
+    tanh soft-cap to the scaled scores before masking (transfusion_pytorch/transfusion.py:358-364). ``check_status=True`` synchronises and
+    raises if the kernel reported a bounded-wait timeout or an out-of-range block index.
+    """
+    B, H = query.shape[:2]
+    qp, kp, vp, block_mask, scale, n_orig, d_orig = _prepare(query, key, value, block_mask, scale)
     out = torch.empty_like(qp)
     lse = torch.empty(B, H, qp.shape[2], dtype=torch.float32, device=qp.device) if return_lse else None
     status = torch.zeros(1, dtype=torch.int32, device=qp.device) if check_status else None
@@ -288,7 +315,7 @@ def omni_attention(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBl
             raise OmniAttnError(f"kernel gave up waiting (status {code:#x}); output is not valid")
         if code & 0xFF == STATUS_BAD_INDEX:
             raise OmniAttnError("kv_indices holds a block id outside [0, num_kv_blocks); the entry was skipped")
-    out = out[:, :, :n_orig]
+    out = out[:, :, :n_orig, :d_orig]
     if return_lse:
         return out, lse[:, :, :n_orig]
     return out
@@ -357,21 +384,9 @@ def omni_attention_autograd(query: Tensor, key: Tensor, value: Tensor, block_mas
                             scale: Optional[float] = None) -> Tensor:
     """``omni_attention`` for training: same inputs and output, differentiable with respect to
     query, key and value (the gradients come from omni_attn_bwd_sm100)."""
-    B, H, Q, D = query.shape
-    if key.shape != (B, H, Q, D) or value.shape != (B, H, Q, D):
-        raise OmniAttnError(f"key/value shape must equal query shape {(B, H, Q, D)} (Q_len == KV_len)")
-    if D not in (64, 128):
-        raise ValueError(f"Unsupported head_dim={D}. Built for sm_100a: 64, 128.")
-    if block_mask.Q_BLOCK_SIZE != 128 or block_mask.KV_BLOCK_SIZE != 128:
-        raise ValueError("Unsupported block size: Q_BLOCK_SIZE and KV_BLOCK_SIZE must be 128.")
-    qp, n_orig = _pad_to_block(query, 128)
-    kp, _ = _pad_to_block(key, 128)
-    vp, _ = _pad_to_block(value, 128)
-    if qp.shape[2] != block_mask.q_len or kp.shape[2] != block_mask.kv_len:
-        raise OmniAttnError(
-            f"padded length {qp.shape[2]} does not match the mask's q_len/kv_len ({block_mask.q_len}/{block_mask.kv_len})")
-    out = _OmniAttentionFn.apply(qp.contiguous(), kp.contiguous(), vp.contiguous(), block_mask, n_orig, scale)
-    return out[:, :, :n_orig]
+    qp, kp, vp, block_mask, scale, n_orig, d_orig = _prepare(query, key, value, block_mask, scale)
+    out = _OmniAttentionFn.apply(qp, kp, vp, block_mask, n_orig, scale)
+    return out[:, :, :n_orig, :d_orig]
 
 
 def default_scale(head_dim: int) -> float:

@@ -100,6 +100,10 @@ def test_operator_refuses_cpu_tensors():
     bm = create_causal_omni_block_mask(1, 1, 128, 128)
     with pytest.raises(ops.OmniAttnError):
         omni_attention(q, q, q, bm)
+    with pytest.raises(ValueError):   # head_dim outside {32, 64, 128}
+        omni_attention(torch.zeros(1, 1, 128, 96, dtype=torch.float16), torch.zeros(1, 1, 128, 96, dtype=torch.float16),
+                       torch.zeros(1, 1, 128, 96, dtype=torch.float16), bm)
+    bm.Q_BLOCK_SIZE = 32              # block sizes outside {64, 128}
+    bm.KV_BLOCK_SIZE = 32
     with pytest.raises(ValueError):
-        omni_attention(torch.zeros(1, 1, 128, 32, dtype=torch.float16), torch.zeros(1, 1, 128, 32, dtype=torch.float16),
-                       torch.zeros(1, 1, 128, 32, dtype=torch.float16), bm)
+        omni_attention(q, q, q, bm)

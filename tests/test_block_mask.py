@@ -157,3 +157,55 @@ def test_mask_from_modality_positions_matches_dense_rule(seq_len):
         assert torch.equal(got[:, h], want)
     with pytest.raises(ValueError):
         create_omni_block_mask_from_modality_positions(mp, 2, 3, 512, 256)
+
+
+def _flex_mask_mod(b, h, q, k):
+    # causal | one bidirectional span | a head-dependent extra span
+    return (k <= q) | ((q >= 100) & (q < 300) & (k < 300)) | ((h == 1) & (q >= 400) & (k < 450))
+
+
+def _flex_dense(n, heads):
+    pos = torch.arange(n)
+    return torch.stack([_flex_mask_mod(torch.tensor(0), torch.tensor(h), pos.view(n, 1), pos.view(1, n))
+                        for h in range(heads)])[None]
+
+
+@pytest.mark.parametrize("flex_block", [128, 64])
+def test_flex_block_mask_converter_attends_where_flex_does(flex_block):
+    """omni_block_mask_from_flex_block_mask (omni-attn-mma/omni_attn_torch.py:226-290): with the element
+    masks materialised the converted mask expands to mask_mod itself, on 128- and 64-wide flex blocks."""
+    from torch.nn.attention.flex_attention import create_block_mask
+
+    from omni_attention_b200.block_mask import omni_block_mask_from_flex_block_mask
+
+    n = 512
+    flex = create_block_mask(_flex_mask_mod, 1, 2, n, n, device="cpu", BLOCK_SIZE=flex_block)
+    bm = omni_block_mask_from_flex_block_mask(flex)
+    assert (bm.Q_BLOCK_SIZE, bm.KV_BLOCK_SIZE) == (128, 128)
+    assert torch.equal(dense_mask_from_blocks(bm), _flex_dense(n, 2))
+    assert torch.equal(dense_mask_from_blocks(bm), orc.to_dense_mask_loops(bm))
+    # the reference's conversion to the letter: flex's partial lists typed PARTIAL without element masks
+    ref_style = omni_block_mask_from_flex_block_mask(flex, materialize_partial=False)
+    assert ref_style.partial_block_masks is None
+    assert torch.equal(ref_style.kv_num_blocks, flex.kv_num_blocks.to(torch.int32))
+    listed = torch.arange(ref_style.kv_indices.shape[3]).view(1, 1, 1, -1) < ref_style.kv_num_blocks.unsqueeze(-1)
+    assert torch.all(ref_style.block_mask_types[listed] == int(BlockMaskType.PARTIAL))
+    assert torch.all(ref_style.block_mask_types[~listed] == int(BlockMaskType.MASKED))
+
+
+def test_retile_64_blocks_to_128_keeps_the_pattern():
+    from omni_attention_b200.block_mask import retile_block_mask
+
+    dense = _flex_dense(512, 2)
+    bm64 = block_mask_from_dense(dense, 64)
+    assert bm64.Q_BLOCK_SIZE == 64 and bm64.kv_indices.shape[2] == 8
+    bm128 = retile_block_mask(bm64, 128)
+    assert bm128.Q_BLOCK_SIZE == 128 and bm128.kv_indices.shape[2:] == (4, 4)
+    assert torch.equal(dense_mask_from_blocks(bm128), dense)
+    # ragged: 300 tokens on 64-blocks (padded to 320) re-tiled for a length padded to 384
+    d300 = torch.zeros(1, 1, 320, 320, dtype=torch.bool)
+    d300[:, :, :300, :300] = torch.tril(torch.ones(300, 300, dtype=torch.bool))
+    r = retile_block_mask(block_mask_from_dense(d300, 64), 128)
+    assert r.q_len == 384
+    assert torch.equal(dense_mask_from_blocks(r)[:, :, :320, :320], d300)
+    assert not bool(dense_mask_from_blocks(r)[:, :, 320:].any())

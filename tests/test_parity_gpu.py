@@ -10,7 +10,8 @@ import torch
 from conftest import GOLDEN_CASES, LSE_ATOL, assert_parity, load_golden
 from omni_attention_b200 import inputs, ops
 from omni_attention_b200.block_mask import (BlockMaskType, OmniBlockMask, create_causal_omni_block_mask,
-                                            dense_mask_from_blocks)
+                                            dense_mask_from_blocks,
+                                            block_mask_from_dense)
 from omni_attention_b200.ops import omni_attention
 from oracle import omni_oracle as orc
 from oracle import scalar
@@ -380,3 +381,48 @@ def test_transfusion_attention_core_with_softcap(cuda_device, D, dtype):
     assert float((plain.float() - out.float()).abs().max()) > 0.05
     with pytest.raises(ops.OmniAttnError):
         omni_attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), bm, kernel="simple", softcap=4.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_head_dim_32_and_64_wide_blocks(cuda_device, dtype):
+    """The reference's launchers also accept head_dim 32 and 64x64 blocks
+    (omni-attn-mma/mma/omni_attn_shared_kv.cu:725-741, :780-888). The operator maps both onto the
+    128x128 / head_dim 64 kernel: the mask is re-tiled, the head dimension zero-padded with the scale
+    kept at 1/sqrt(32)."""
+    torch.manual_seed(8)
+    n = 640
+    pos = torch.arange(n)
+    dense = (pos.view(1, n) <= pos.view(n, 1)) | ((pos.view(n, 1) >= 70) & (pos.view(n, 1) < 330) & (pos.view(1, n) < 330))
+    dense = dense[None, None].expand(1, 2, n, n).contiguous()
+    bm64 = block_mask_from_dense(dense, 64)
+    assert bm64.Q_BLOCK_SIZE == 64
+    q, k, v = (torch.randn(1, 2, n, 32).to(dtype) for _ in range(3))
+    out, lse = omni_attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), bm64, return_lse=True)
+    assert out.shape == (1, 2, n, 32)
+    ref_out, ref_lse = orc.attention_dense_mask(q.float(), k.float(), v.float(), orc.to_score_mask(dense))
+    assert_parity(out, lse, ref_out, ref_lse, "D=32, 64-wide blocks")
+
+
+def test_flex_block_mask_through_the_kernel(cuda_device):
+    """A flex_attention BlockMask (built on the CPU, no Triton involved) converted with
+    omni_block_mask_from_flex_block_mask drives the kernel to the dense-mask result."""
+    from torch.nn.attention.flex_attention import create_block_mask
+
+    from omni_attention_b200.block_mask import omni_block_mask_from_flex_block_mask
+
+    def mask_mod(b, h, q, k):
+        return (k <= q) | ((q >= 200) & (q < 500) & (k < 500))
+
+    n = 768
+    flex = create_block_mask(mask_mod, 1, 1, n, n, device="cpu", BLOCK_SIZE=128)
+    bm = omni_block_mask_from_flex_block_mask(flex)
+    bm = OmniBlockMask(bm.kv_num_blocks.expand(1, 4, -1).contiguous(), bm.kv_indices.expand(1, 4, -1, -1).contiguous(),
+                       bm.block_mask_types.expand(1, 4, -1, -1).contiguous(), n, n, 128, 128,
+                       bm.partial_block_mask_indices.expand(1, 4, -1, -1).contiguous(), bm.partial_block_masks)
+    torch.manual_seed(9)
+    q, k, v = (torch.randn(1, 4, n, 64).bfloat16() for _ in range(3))
+    out, lse = run(q, k, v, bm, cuda_device)
+    pos = torch.arange(n)
+    dense = mask_mod(0, 0, pos.view(n, 1), pos.view(1, n))
+    ref_out, ref_lse = orc.attention_dense_mask(q.float(), k.float(), v.float(), orc.to_score_mask(dense)[None, None])
+    assert_parity(out, lse, ref_out, ref_lse, "flex mask")
