@@ -132,6 +132,19 @@ __device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uin
   }
 }
 
+// The same with the 16-bit A operand stored as two runs of 32 TMEM columns, 64 columns apart
+// (contraction indices [0,64) at a_region + a_off, [64,128) at a_region + 64 + a_off): the layout the
+// tile kernels use so that each thread writes P / dS only over score columns it has read itself.
+template <int D>
+__device__ __forceinline__ void bwd_mma_ts_split(uint32_t d_tmem, uint32_t a_region, uint32_t a_off, uint32_t sB,
+                                                 uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int k = 0; k < kBlock / 16; ++k) {
+    umma_ts(d_tmem, a_region + 64 * (k / 4) + a_off + 8 * (k % 4),
+            umma_smem_desc_sw128(sB + k * 2048, BwdCfg<D>::kChunkBytes, 1024), idesc, (accumulate || k > 0) ? 1u : 0u);
+  }
+}
+
 // One accumulator row (32-column chunks [kFirstChunk, kEndChunk) of it) out of TMEM, times `mul`, as
 // 16-bit values to global memory (zeros when `have_acc` is false).
 template <int D, bool BF16, int kFirstChunk = 0, int kEndChunk = D / 32>
@@ -204,8 +217,8 @@ __device__ __forceinline__ float lse_to_log2(float lse) {
 // ---------------------------------------------------------------------------------------------
 // 2. dK, dV. One CTA per (KV block, batch*head), see bwd_decode_cta. Threads t and t + 128 own key row t of the block
 // (query columns [0,64) and [64,128)).
-// TMEM: S^T [0,128)  dP^T [128,256)  dV [256,256+D)  dK [384,384+D). P^T (16-bit) is written over
-// the first 64 columns of S^T, dS^T over the first 64 columns of dP^T.
+// TMEM: two score regions [0,128) and [128,256) that S^T and dP^T swap between visits, dV
+// [256,256+D), dK [384,384+D). P^T and dS^T (16-bit) are written over S^T.
 // ---------------------------------------------------------------------------------------------
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -267,8 +280,6 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  const uint32_t tSt = tmem_base;
-  const uint32_t tdPt = tmem_base + 128;
   const uint32_t tdV = tmem_base + 256;
   const uint32_t tdK = tmem_base + 384;
   constexpr int fmt = BF16 ? 1 : 0;
@@ -288,15 +299,16 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     code = code_s[qb];
     return qb;
   };
-  // Stage a Q block: TMA for Q and dO (thread 0), LSE and delta by every thread for its own row.
-  auto stage_q_block = [&](int qb, int stage) {
-    if (tid == kBwdIssuer) {
-      const uint32_t bar = bar_ld + 8 * stage;
-      mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
-      const int y = static_cast<int>(row0 + qb * kBlock);
-      bwd_load_tile<D>(sQ + stage * Cfg::kTileBytes, &tmQ, bar, y);
-      bwd_load_tile<D>(sdO + stage * Cfg::kTileBytes, &tmdO, bar, y);
-    }
+  // Staging of a Q block: the tiles (TMA, issuer thread) and the LSE / delta vectors (threads 0-127)
+  // become possible at different times, hence two pieces.
+  auto stage_tiles = [&](int qb, int stage) {
+    const uint32_t bar = bar_ld + 8 * stage;
+    mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
+    const int y = static_cast<int>(row0 + qb * kBlock);
+    bwd_load_tile<D>(sQ + stage * Cfg::kTileBytes, &tmQ, bar, y);
+    bwd_load_tile<D>(sdO + stage * Cfg::kTileBytes, &tmdO, bar, y);
+  };
+  auto stage_vectors = [&](int qb, int stage) {
     if (tid < kBlock) {
       const int q_abs = qb * kBlock + tid;
       const long long row = row0 + q_abs;
@@ -305,48 +317,45 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       delta_s[stage * kBlock + tid] = live ? -__ldg(p.delta + row) : 0.f;                   // negated
     }
   };
+  // Visit i keeps S^T in TMEM region (i & 1) and dP^T in the other one (128 columns each). The
+  // per-element pass writes P^T and dS^T over S^T only, so the dP^T region is free again as soon
+  // as that pass ends and takes the S^T of visit i + 1 while dV / dK of visit i are still running.
+  auto issue_scores = [&](int i) {   // issuer thread
+    const int stage = i & 1;
+    mbar_wait(bar_ld + 8 * stage, static_cast<uint32_t>((i >> 1) & 1), abort_flag, p.f.status, 51);
+    tc_fence_after();
+    bwd_mma_ss<D>(tmem_base + 128 * (i & 1), sK, sQ + stage * Cfg::kTileBytes, idesc_ss);            // S^T  = K Q^T
+    bwd_mma_ss<D>(tmem_base + 128 * ((i & 1) ^ 1), sV, sdO + stage * Cfg::kTileBytes, idesc_ss);    // dP^T = V dO^T
+    tc_commit(bar_s);
+  };
 
   uint32_t code_cur = 0u, code_next = 0u;
   int qb_cur = visited_at(0, code_cur);
-  if (qb_cur < nq) {
+  if (n_vis > 0) {
+    uint32_t unused;
     if (tid == kBwdIssuer) {
       mbar_expect_tx(bar_kv, 2 * Cfg::kTileBytes);
       const int y = static_cast<int>(row0 + kvb * kBlock);
       bwd_load_tile<D>(sK, &tmK, bar_kv, y);
       bwd_load_tile<D>(sV, &tmV, bar_kv, y);
+      stage_tiles(qb_cur, 0);
+      if (n_vis > 1) stage_tiles(visited_at(1, unused), 1);
+      mbar_wait(bar_kv, 0, abort_flag, p.f.status, 50);
+      issue_scores(0);
     }
-    stage_q_block(qb_cur, 0);
+    stage_vectors(qb_cur, 0);
+    if (n_vis > 1) stage_vectors(visited_at(1, unused), 1);
   }
-  __syncthreads();   // the first block's LSE / delta vectors are read by every thread
+  __syncthreads();   // the LSE / delta vectors are read by every thread
   const int k_abs = kvb * kBlock + t;
   const bool key_live = k_abs < p.f.seqlen_orig;
+  const float2 c2 = make_float2(p.f.scale_log2, p.f.scale_log2);
 
-#ifdef OMNI_BWD_PROFILE
-  long long acc_t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  long long t_prev = clock64();
-#define OMNI_BSTAMP(i) if (tid == 0 || tid == kBwdIssuer) { const long long t_now = clock64(); acc_t[i] += t_now - t_prev; t_prev = t_now; }
-#else
-#define OMNI_BSTAMP(i)
-#endif
-  int it = 0;
-  while (qb_cur < nq) {
-    OMNI_BSTAMP(0);
+  for (int it = 0; it < n_vis; ++it) {
     const int stage = it & 1;
-    const uint32_t ph = static_cast<uint32_t>(it & 1);
-    if (tid == kBwdIssuer) {
-      if (it == 0) mbar_wait(bar_kv, 0, abort_flag, p.f.status, 50);
-      mbar_wait(bar_ld + 8 * stage, static_cast<uint32_t>((it >> 1) & 1), abort_flag, p.f.status, 51);
-      tc_fence_after();
-      OMNI_BSTAMP(3);
-      bwd_mma_ss<D>(tSt, sK, sQ + stage * Cfg::kTileBytes, idesc_ss);     // S^T  = K Q^T
-      bwd_mma_ss<D>(tdPt, sV, sdO + stage * Cfg::kTileBytes, idesc_ss);   // dP^T = V dO^T
-      tc_commit(bar_s);
-      OMNI_BSTAMP(1);
-    }
-    // Stage the next Q block while the MMAs run. The other stage was last read by the MMAs of the
-    // previous iteration, which have completed.
+    const uint32_t tS = tmem_base + 128 * (it & 1);          // S^T, then P^T / dS^T
+    const uint32_t tdP = tmem_base + 128 * ((it & 1) ^ 1);   // dP^T
     const int qb_next = visited_at(it + 1, code_next);
-    if (qb_next < nq) stage_q_block(qb_next, stage ^ 1);
 
     // Allow-bits of this thread's key over its 64 query rows of the block (bit r of word w = query
     // row 64 * half + 32 * w + r).
@@ -387,94 +396,94 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
     }
 
-    uint32_t pp[2][16], dd[2][16];
-    OMNI_BSTAMP(2);
     if (compute) {
-    mbar_wait_warp(bar_s, ph, abort_flag, p.f.status, 52);
-    tc_fence_after();
-    OMNI_BSTAMP(3);
-    const float* lse_c = lse_s + stage * kBlock + 64 * half;
-    const float* del_c = delta_s + stage * kBlock + 64 * half;
-    const float2 c2 = make_float2(p.f.scale_log2, p.f.scale_log2);
-    // two copies of the loop, so that tiles without any masking (the bulk) carry no select at all
-    auto tile_math = [&](auto masked_c) {
-      constexpr bool kMasked = decltype(masked_c)::value;
+      mbar_wait_warp(bar_s, static_cast<uint32_t>(it & 1), abort_flag, p.f.status, 52);
+      tc_fence_after();
+      const float* lse_c = lse_s + stage * kBlock + 64 * half;
+      const float* del_c = delta_s + stage * kBlock + 64 * half;
+      const uint32_t my_s = tS + lane_base + 64 * half;
+      const uint32_t my_dp = tdP + lane_base + 64 * half;
+      uint32_t dd0[16];
+      // two copies of the loop, so that tiles without any masking (the bulk) carry no select at all
+      auto tile_math = [&](auto masked_c) {
+        constexpr bool kMasked = decltype(masked_c)::value;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rd[32];
-        tmem_ld32(tSt + lane_base + 64 * half + 32 * c, rs);
-        tmem_ld32(tdPt + lane_base + 64 * half + 32 * c, rd);
-        tc_wait_ld();
-        const uint32_t aw = allow[c];
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rs[32], rd[32];
+          tmem_ld32(my_s + 32 * c, rs);
+          tmem_ld32(my_dp + 32 * c, rd);
+          tc_wait_ld();
+          uint32_t pp[16], dd[16];
+          const uint32_t aw = allow[c];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float2 nl = *reinterpret_cast<const float2*>(lse_c + 32 * c + 2 * j);
-          const float2 nd = *reinterpret_cast<const float2*>(del_c + 32 * c + 2 * j);
-          const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), c2, nl);
-          float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-          float2 ds = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd));
-          if constexpr (kMasked) {
-            const bool ok0 = (aw >> (2 * j)) & 1u, ok1 = (aw >> (2 * j + 1)) & 1u;
-            pr.x = ok0 ? pr.x : 0.f;
-            pr.y = ok1 ? pr.y : 0.f;
-            ds.x = ok0 ? ds.x : 0.f;
-            ds.y = ok1 ? ds.y : 0.f;
+          for (int j = 0; j < 16; ++j) {
+            const float2 nl = *reinterpret_cast<const float2*>(lse_c + 32 * c + 2 * j);
+            const float2 nd = *reinterpret_cast<const float2*>(del_c + 32 * c + 2 * j);
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), c2, nl);
+            float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+            float2 ds = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd));
+            if constexpr (kMasked) {
+              const bool ok0 = (aw >> (2 * j)) & 1u, ok1 = (aw >> (2 * j + 1)) & 1u;
+              pr.x = ok0 ? pr.x : 0.f;
+              pr.y = ok1 ? pr.y : 0.f;
+              ds.x = ok0 ? ds.x : 0.f;
+              ds.y = ok1 ? ds.y : 0.f;
+            }
+            pp[j] = pack2<BF16>(pr.x, pr.y);
+            dd[j] = pack2<BF16>(ds.x, ds.y);
           }
-          pp[c][j] = pack2<BF16>(pr.x, pr.y);
-          dd[c][j] = pack2<BF16>(ds.x, ds.y);
-        }
-      }
-    };
-    if (masked) {   // uniform over the CTA
-      tile_math(std::true_type{});
-    } else {
-      tile_math(std::false_type{});
-    }
-    }
-    OMNI_BSTAMP(4);
-    // The packed P^T / dS^T rows land on columns [0,64) of S^T / dP^T, which the other warpgroup may
-    // still be reading: everybody reads first, then everybody writes.
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    if (compute) {
+          // P^T over this thread's S^T columns [0,32) of its half, dS^T over [32,64): chunk c has
+          // been read completely (chunk 0 covers [0,32)), and nobody else touches these columns
+          tmem_st16(my_s + 16 * c, pp);
+          if (c == 1) {
+            tmem_st16(my_s + 32, dd0);
+            tmem_st16(my_s + 48, dd);
+          } else {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_st16(tSt + lane_base + 32 * half + 16 * c, pp[c]);
-        tmem_st16(tdPt + lane_base + 32 * half + 16 * c, dd[c]);
+            for (int j = 0; j < 16; ++j) dd0[j] = dd[j];
+          }
+        }
+      };
+      if (masked) {   // uniform over the CTA
+        tile_math(std::true_type{});
+      } else {
+        tile_math(std::false_type{});
       }
       tc_wait_st();
     }
     tc_fence_before();
     __syncthreads();
-    OMNI_BSTAMP(5);
 
     if (tid == kBwdIssuer) {
       tc_fence_after();
-      bwd_mma_ts<D>(tdV, tSt, sdO + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dV += P^T dO
-      bwd_mma_ts<D>(tdK, tdPt, sQ + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dK += dS^T Q
+      bwd_mma_ts_split<D>(tdV, tS, 0, sdO + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dV += P^T dO
+      bwd_mma_ts_split<D>(tdK, tS, 32, sQ + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dK += dS^T Q
       tc_commit(bar_acc);
+      if (it + 1 < n_vis) issue_scores(it + 1);
+      if (it + 2 < n_vis) {
+        // the tiles of this visit are free once its dV / dK MMAs have completed
+        mbar_wait(bar_acc, static_cast<uint32_t>(it & 1), abort_flag, p.f.status, 53);
+        uint32_t unused;
+        stage_tiles(visited_at(it + 2, unused), stage);
+      }
     }
-    OMNI_BSTAMP(6);
-    if (compute) {
-      mbar_wait_warp(bar_acc, ph, abort_flag, p.f.status, 53);
-    } else if (tid == kBwdIssuer) {
-      mbar_wait(bar_acc, ph, abort_flag, p.f.status, 53);
+    if (it + 2 < n_vis) {
+      uint32_t unused;
+      stage_vectors(visited_at(it + 2, unused), stage);   // read two barriers from here
     }
-    tc_fence_after();
-    OMNI_BSTAMP(7);
     qb_cur = qb_next;
     code_cur = code_next;
-    ++it;
+  }
+  const int it = n_vis;
+  if (n_vis > 0) {
+    if (compute) {
+      mbar_wait_warp(bar_acc, static_cast<uint32_t>((n_vis - 1) & 1), abort_flag, p.f.status, 54);
+    } else if (tid == kBwdIssuer) {
+      mbar_wait(bar_acc, static_cast<uint32_t>((n_vis - 1) & 1), abort_flag, p.f.status, 54);
+    }
+    tc_fence_after();
   }
 
-#ifdef OMNI_BWD_PROFILE
-  if ((tid == 0 || tid == kBwdIssuer) && p.f.status != nullptr) {
-    unsigned long long* prof = reinterpret_cast<unsigned long long*>(p.f.status + 4) + (tid == 0 ? 0 : 10);
-    for (int i = 0; i < 8; ++i) atomicAdd(prof + i, static_cast<unsigned long long>(acc_t[i]));
-    atomicAdd(prof + 8, static_cast<unsigned long long>(it));
-  }
-#endif
   const long long out_row = row0 + k_abs;
   if (compute && half == 0) {
     bwd_store_row<D, BF16>(tdV + lane_base, it > 0, 1.f, p.dv, out_row);
@@ -490,8 +499,8 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 // ---------------------------------------------------------------------------------------------
 // 3. dQ. One CTA per (Q block, batch*head), see bwd_decode_cta. Threads t and t + 128 own query row t of the block
 // (key columns [0,64) and [64,128)).
-// TMEM: S [0,128)  dP [128,256)  dQ [256,256+D). dS (16-bit) is written over the first 64 columns
-// of dP.
+// TMEM: two score regions [0,128) and [128,256) that S and dP swap between visits, dQ [256,256+D).
+// dS (16-bit) is written over S.
 // ---------------------------------------------------------------------------------------------
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -550,8 +559,6 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  const uint32_t tS = tmem_base;
-  const uint32_t tdP = tmem_base + 128;
   const uint32_t tdQ = tmem_base + 256;
   constexpr int fmt = BF16 ? 1 : 0;
   constexpr uint32_t idesc_ss = umma_idesc_f16(128, 128, fmt, 0);
@@ -570,14 +577,22 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     code = code_s[kvb];
     return kvb;
   };
-  auto stage_kv_block = [&](int kvb, int stage) {
-    if (tid == kBwdIssuer) {
-      const uint32_t bar = bar_ld + 8 * stage;
-      mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
-      const int y = static_cast<int>(row0 + kvb * kBlock);
-      bwd_load_tile<D>(sK + stage * Cfg::kTileBytes, &tmK, bar, y);
-      bwd_load_tile<D>(sV + stage * Cfg::kTileBytes, &tmV, bar, y);
-    }
+  auto stage_tiles = [&](int kvb, int stage) {   // issuer thread
+    const uint32_t bar = bar_ld + 8 * stage;
+    mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
+    const int y = static_cast<int>(row0 + kvb * kBlock);
+    bwd_load_tile<D>(sK + stage * Cfg::kTileBytes, &tmK, bar, y);
+    bwd_load_tile<D>(sV + stage * Cfg::kTileBytes, &tmV, bar, y);
+  };
+  // Visit i keeps S in TMEM region (i & 1) and dP in the other one; dS is written over S, so the dP
+  // region takes the S of visit i + 1 while dQ of visit i is still running.
+  auto issue_scores = [&](int i) {   // issuer thread
+    const int stage = i & 1;
+    mbar_wait(bar_ld + 8 * stage, static_cast<uint32_t>((i >> 1) & 1), abort_flag, p.f.status, 61);
+    tc_fence_after();
+    bwd_mma_ss<D>(tmem_base + 128 * (i & 1), sQ, sK + stage * Cfg::kTileBytes, idesc_ss);            // S  = Q K^T
+    bwd_mma_ss<D>(tmem_base + 128 * ((i & 1) ^ 1), sdO, sV + stage * Cfg::kTileBytes, idesc_ss);    // dP = dO V^T
+    tc_commit(bar_s);
   };
 
   const int q_abs = qb * kBlock + t;
@@ -592,75 +607,63 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   uint32_t code_cur = 0u, code_next = 0u;
   int kvb_cur = visited_at(0, code_cur);
-  if (kvb_cur < nq) {
-    if (tid == kBwdIssuer) {
-      mbar_expect_tx(bar_q, 2 * Cfg::kTileBytes);
-      const int y = static_cast<int>(row0 + qb * kBlock);
-      bwd_load_tile<D>(sQ, &tmQ, bar_q, y);
-      bwd_load_tile<D>(sdO, &tmdO, bar_q, y);
-    }
-    stage_kv_block(kvb_cur, 0);
+  if (n_vis > 0 && tid == kBwdIssuer) {
+    uint32_t unused;
+    mbar_expect_tx(bar_q, 2 * Cfg::kTileBytes);
+    const int y = static_cast<int>(row0 + qb * kBlock);
+    bwd_load_tile<D>(sQ, &tmQ, bar_q, y);
+    bwd_load_tile<D>(sdO, &tmdO, bar_q, y);
+    stage_tiles(kvb_cur, 0);
+    if (n_vis > 1) stage_tiles(visited_at(1, unused), 1);
+    mbar_wait(bar_q, 0, abort_flag, p.f.status, 60);
+    issue_scores(0);
   }
 
-  int it = 0;
-  while (kvb_cur < nq) {
+  for (int it = 0; it < n_vis; ++it) {
     const int stage = it & 1;
-    const uint32_t ph = static_cast<uint32_t>(it & 1);
-    if (tid == kBwdIssuer) {
-      if (it == 0) mbar_wait(bar_q, 0, abort_flag, p.f.status, 60);
-      mbar_wait(bar_ld + 8 * stage, static_cast<uint32_t>((it >> 1) & 1), abort_flag, p.f.status, 61);
-      tc_fence_after();
-      bwd_mma_ss<D>(tS, sQ, sK + stage * Cfg::kTileBytes, idesc_ss);     // S  = Q K^T
-      bwd_mma_ss<D>(tdP, sdO, sV + stage * Cfg::kTileBytes, idesc_ss);   // dP = dO V^T
-      tc_commit(bar_s);
-    }
-    // stage the next KV block while the MMAs run
+    const uint32_t tS = tmem_base + 128 * (it & 1);          // S, then dS
+    const uint32_t tdP = tmem_base + 128 * ((it & 1) ^ 1);   // dP
     const int kvb_next = visited_at(it + 1, code_next);
-    if (kvb_next < nq) stage_kv_block(kvb_next, stage ^ 1);
 
     const bool masked = (code_cur & kCodeTypeMask) != kTypeFull || (code_cur & kCodeClip);
     uint32_t allow[4] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
     if (masked) build_allow(p.f, code_cur, kvb_cur, t, allow);
 
-    uint32_t dd[2][16];
     if (compute) {
-    mbar_wait_warp(bar_s, ph, abort_flag, p.f.status, 62);
-    tc_fence_after();
-    auto tile_math = [&](auto masked_c) {
-      constexpr bool kMasked = decltype(masked_c)::value;
+      mbar_wait_warp(bar_s, static_cast<uint32_t>(it & 1), abort_flag, p.f.status, 62);
+      tc_fence_after();
+      const uint32_t my_s = tS + lane_base + 64 * half;
+      const uint32_t my_dp = tdP + lane_base + 64 * half;
+      auto tile_math = [&](auto masked_c) {
+        constexpr bool kMasked = decltype(masked_c)::value;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rd[32];
-        tmem_ld32(tS + lane_base + 64 * half + 32 * c, rs);
-        tmem_ld32(tdP + lane_base + 64 * half + 32 * c, rd);
-        tc_wait_ld();
-        const uint32_t aw = allow[2 * half + c];
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rs[32], rd[32];
+          tmem_ld32(my_s + 32 * c, rs);
+          tmem_ld32(my_dp + 32 * c, rd);
+          tc_wait_ld();
+          uint32_t dd[16];
+          const uint32_t aw = allow[2 * half + c];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), c2, nl2);
-          const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-          float2 ds = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd2));
-          if constexpr (kMasked) {
-            ds.x = ((aw >> (2 * j)) & 1u) ? ds.x : 0.f;
-            ds.y = ((aw >> (2 * j + 1)) & 1u) ? ds.y : 0.f;
+          for (int j = 0; j < 16; ++j) {
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), c2, nl2);
+            const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+            float2 ds = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd2));
+            if constexpr (kMasked) {
+              ds.x = ((aw >> (2 * j)) & 1u) ? ds.x : 0.f;
+              ds.y = ((aw >> (2 * j + 1)) & 1u) ? ds.y : 0.f;
+            }
+            dd[j] = pack2<BF16>(ds.x, ds.y);
           }
-          dd[c][j] = pack2<BF16>(ds.x, ds.y);
+          // dS over this thread's S columns [0,32) of its half: columns it has read already
+          tmem_st16(my_s + 16 * c, dd);
         }
+      };
+      if (masked) {   // uniform over the CTA
+        tile_math(std::true_type{});
+      } else {
+        tile_math(std::false_type{});
       }
-    };
-    if (masked) {   // uniform over the CTA
-      tile_math(std::true_type{});
-    } else {
-      tile_math(std::false_type{});
-    }
-    }
-    // dS lands on columns [0,64) of dP, which the other warpgroup may still be reading
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    if (compute) {
-#pragma unroll
-      for (int c = 0; c < 2; ++c) tmem_st16(tdP + lane_base + 32 * half + 16 * c, dd[c]);
       tc_wait_st();
     }
     tc_fence_before();
@@ -668,18 +671,26 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     if (tid == kBwdIssuer) {
       tc_fence_after();
-      bwd_mma_ts<D>(tdQ, tdP, sK + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dQ += dS K
+      bwd_mma_ts_split<D>(tdQ, tS, 0, sK + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dQ += dS K
       tc_commit(bar_acc);
+      if (it + 1 < n_vis) issue_scores(it + 1);
+      if (it + 2 < n_vis) {
+        mbar_wait(bar_acc, static_cast<uint32_t>(it & 1), abort_flag, p.f.status, 63);
+        uint32_t unused;
+        stage_tiles(visited_at(it + 2, unused), stage);
+      }
     }
-    if (compute) {
-      mbar_wait_warp(bar_acc, ph, abort_flag, p.f.status, 63);
-    } else if (tid == kBwdIssuer) {
-      mbar_wait(bar_acc, ph, abort_flag, p.f.status, 63);
-    }
-    tc_fence_after();
     kvb_cur = kvb_next;
     code_cur = code_next;
-    ++it;
+  }
+  const int it = n_vis;
+  if (n_vis > 0) {
+    if (compute) {
+      mbar_wait_warp(bar_acc, static_cast<uint32_t>((n_vis - 1) & 1), abort_flag, p.f.status, 64);
+    } else if (tid == kBwdIssuer) {
+      mbar_wait(bar_acc, static_cast<uint32_t>((n_vis - 1) & 1), abort_flag, p.f.status, 64);
+    }
+    tc_fence_after();
   }
 
   if (compute && half == 0) {
