@@ -239,6 +239,18 @@ int omni_attn_bwd_sm100(const void* q, const void* k, const void* v, const void*
                         float scale, void* cuda_stream, int32_t* device_status_or_null, void* workspace,
                         long long workspace_bytes);
 
+/* omni_attn_bwd_sm100 for a forward that was run with a tanh soft-cap (omni_attn_fwd_ex_sm100 with the
+ * same softcap > 0; transfusion_pytorch/transfusion.py:298-299, :967): the chain rule adds the factor
+ * 1 - tanh^2(score * scale / softcap) to dS. softcap == 0 is omni_attn_bwd_sm100. */
+int omni_attn_bwd_ex_sm100(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                           const void* d_o, void* dq, void* dk, void* dv, const int32_t* kv_num_blocks,
+                           const int32_t* kv_indices, const int32_t* block_mask_types,
+                           const int32_t* partial_idx_or_null, const uint8_t* partial_bool_or_null,
+                           const uint32_t* partial_bits_or_null, int B, int H, int seqlen_padded, int seqlen_orig,
+                           int head_dim, int q_block, int kv_block, int max_blocks, int num_partial, int dtype,
+                           float scale, void* cuda_stream, int32_t* device_status_or_null, void* workspace,
+                           long long workspace_bytes, float softcap);
+
 /* Text for an OMNI_ERR_* code; the pointer is static storage. */
 const char* omni_attn_error_string(int code);
 

@@ -160,7 +160,8 @@ int backward(const void* q, const void* k, const void* v, const void* o, const f
              const int32_t* types, const int32_t* partial_idx, const uint8_t* partial_bool,
              const uint32_t* partial_bits, int B, int H, int seqlen_padded, int seqlen_orig, int head_dim,
              int q_block, int kv_block, int max_blocks, int num_partial, int dtype, float scale, void* stream,
-             int32_t* status, void* workspace, long long workspace_bytes) {
+             int32_t* status, void* workspace, long long workspace_bytes, float softcap = 0.f) {
+  if (softcap < 0.f || softcap != softcap) return OMNI_ERR_SOFTCAP;
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || lse == nullptr || d_o == nullptr ||
       dq == nullptr || dk == nullptr || dv == nullptr || kv_num_blocks == nullptr || kv_indices == nullptr ||
       types == nullptr || workspace == nullptr) {
@@ -218,8 +219,8 @@ int backward(const void* q, const void* k, const void* v, const void* o, const f
   p.f.scale = scale > 0.f ? scale : 1.f / std::sqrt(static_cast<float>(head_dim));
   p.f.scale_log2 = p.f.scale * 1.4426950408889634f;
   p.f.inv_scale_log2 = 1.f / p.f.scale_log2;
-  p.f.cap_in = 0.f;
-  p.f.cap_out = 0.f;
+  p.f.cap_in = softcap > 0.f ? p.f.scale / softcap : 0.f;
+  p.f.cap_out = softcap > 0.f ? softcap / p.f.scale : 0.f;
   // Q, K, V and dO of a head group share L2: half as many heads per group as in the forward pass
   p.f.group_heads = group_heads_for(BH, seqlen_padded, head_dim) / 2 > 0 ? group_heads_for(BH, seqlen_padded, head_dim) / 2 : 1;
   p.f.num_units = 0;
@@ -427,6 +428,20 @@ int omni_attn_bwd_sm100(const void* q, const void* k, const void* v, const void*
                         partial_idx_or_null, partial_bool_or_null, partial_bits_or_null, B, H, seqlen_padded,
                         seqlen_orig, head_dim, q_block, kv_block, max_blocks, num_partial, dtype, scale,
                         cuda_stream, device_status_or_null, workspace, workspace_bytes);
+}
+
+int omni_attn_bwd_ex_sm100(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                           const void* d_o, void* dq, void* dk, void* dv, const int32_t* kv_num_blocks,
+                           const int32_t* kv_indices, const int32_t* block_mask_types,
+                           const int32_t* partial_idx_or_null, const uint8_t* partial_bool_or_null,
+                           const uint32_t* partial_bits_or_null, int B, int H, int seqlen_padded, int seqlen_orig,
+                           int head_dim, int q_block, int kv_block, int max_blocks, int num_partial, int dtype,
+                           float scale, void* cuda_stream, int32_t* device_status_or_null, void* workspace,
+                           long long workspace_bytes, float softcap) {
+  return omni::backward(q, k, v, o, lse, d_o, dq, dk, dv, kv_num_blocks, kv_indices, block_mask_types,
+                        partial_idx_or_null, partial_bool_or_null, partial_bits_or_null, B, H, seqlen_padded,
+                        seqlen_orig, head_dim, q_block, kv_block, max_blocks, num_partial, dtype, scale,
+                        cuda_stream, device_status_or_null, workspace, workspace_bytes, softcap);
 }
 
 const char* omni_attn_error_string(int code) {

@@ -193,6 +193,20 @@ __device__ __forceinline__ int bwd_build_visit_list(const uint32_t* src, long lo
   return *n_vis_s;
 }
 
+// Tanh soft-cap in the backward pass (the forward's soft_cap_scores): the raw score s stands for the
+// capped scaled score softcap * tanh(s * scale / softcap), whose derivative with respect to the
+// scaled raw score is 1 - tanh^2. Replaces the pair of raw scores by their capped raw-equivalents
+// (cap_out * tanh) and returns the two derivative factors.
+__device__ __forceinline__ float2 bwd_soft_cap(float2& s, float cap_in, float cap_out) {
+  const float k = cap_in * 2.8853900817779268f;   // 2 * log2(e)
+  float r0, r1;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(ex2_approx(s.x * k) + 1.f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(ex2_approx(s.y * k) + 1.f));
+  const float t0 = fmaf(-2.f, r0, 1.f), t1 = fmaf(-2.f, r1, 1.f);
+  s = make_float2(cap_out * t0, cap_out * t1);
+  return make_float2(fmaf(-t0, t0, 1.f), fmaf(-t1, t1, 1.f));
+}
+
 // CTA index -> (block, batch*head) for the two tile kernels. Heads are taken in groups of
 // `group_heads` (sized on the host so that a group's Q, K, V and dO stay in L2 together); inside a
 // group the blocks run from the longest lists to the shortest for causal-like masks (`descending`:
@@ -220,7 +234,7 @@ __device__ __forceinline__ float lse_to_log2(float lse) {
 // TMEM: two score regions [0,128) and [128,256) that S^T and dP^T swap between visits, dV
 // [256,256+D), dK [384,384+D). P^T and dS^T (16-bit) are written over S^T.
 // ---------------------------------------------------------------------------------------------
-template <int D, bool BF16>
+template <int D, bool BF16, bool SOFTCAP>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -419,9 +433,13 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int j = 0; j < 16; ++j) {
             const float2 nl = *reinterpret_cast<const float2*>(lse_c + 32 * c + 2 * j);
             const float2 nd = *reinterpret_cast<const float2*>(del_c + 32 * c + 2 * j);
-            const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), c2, nl);
+            float2 sc = make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1]));
+            float2 slope;
+            if constexpr (SOFTCAP) slope = bwd_soft_cap(sc, p.f.cap_in, p.f.cap_out);
+            const float2 x = __ffma2_rn(sc, c2, nl);
             float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
             float2 ds = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd));
+            if constexpr (SOFTCAP) ds = __fmul2_rn(ds, slope);
             if constexpr (kMasked) {
               const bool ok0 = (aw >> (2 * j)) & 1u, ok1 = (aw >> (2 * j + 1)) & 1u;
               pr.x = ok0 ? pr.x : 0.f;
@@ -502,7 +520,7 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 // TMEM: two score regions [0,128) and [128,256) that S and dP swap between visits, dQ [256,256+D).
 // dS (16-bit) is written over S.
 // ---------------------------------------------------------------------------------------------
-template <int D, bool BF16>
+template <int D, bool BF16, bool SOFTCAP>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -646,9 +664,13 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const uint32_t aw = allow[2 * half + c];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), c2, nl2);
+            float2 sc = make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1]));
+            float2 slope;
+            if constexpr (SOFTCAP) slope = bwd_soft_cap(sc, p.f.cap_in, p.f.cap_out);
+            const float2 x = __ffma2_rn(sc, c2, nl2);
             const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
             float2 ds = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd2));
+            if constexpr (SOFTCAP) ds = __fmul2_rn(ds, slope);
             if constexpr (kMasked) {
               ds.x = ((aw >> (2 * j)) & 1u) ? ds.x : 0.f;
               ds.y = ((aw >> (2 * j + 1)) & 1u) ? ds.y : 0.f;
@@ -704,12 +726,12 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 0) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool SOFTCAP>
 static cudaError_t launch_bwd_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
                                 const CUtensorMap& tmdO, const BwdParams& p, cudaStream_t stream) {
   using Cfg = BwdCfg<D>;
-  auto dkdv = omni_bwd_dkdv_kernel<D, BF16>;
-  auto dq = omni_bwd_dq_kernel<D, BF16>;
+  auto dkdv = omni_bwd_dkdv_kernel<D, BF16, SOFTCAP>;
+  auto dq = omni_bwd_dq_kernel<D, BF16, SOFTCAP>;
   static bool attr_dkdv[64] = {};
   static bool attr_dq[64] = {};
   cudaError_t e = ensure_smem_attr(dkdv, Cfg::kSmemBytes, attr_dkdv);
@@ -730,12 +752,21 @@ static cudaError_t launch_bwd_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, 
 
 cudaError_t launch_bwd(int head_dim, bool bf16, const CUtensorMap& tmQ, const CUtensorMap& tmK,
                        const CUtensorMap& tmV, const CUtensorMap& tmdO, const BwdParams& p, cudaStream_t stream) {
+  const bool cap = p.f.cap_out != 0.f;
   if (head_dim == 64) {
-    return bf16 ? launch_bwd_t<64, true>(tmQ, tmK, tmV, tmdO, p, stream)
-                : launch_bwd_t<64, false>(tmQ, tmK, tmV, tmdO, p, stream);
+    if (cap) {
+      return bf16 ? launch_bwd_t<64, true, true>(tmQ, tmK, tmV, tmdO, p, stream)
+                  : launch_bwd_t<64, false, true>(tmQ, tmK, tmV, tmdO, p, stream);
+    }
+    return bf16 ? launch_bwd_t<64, true, false>(tmQ, tmK, tmV, tmdO, p, stream)
+                : launch_bwd_t<64, false, false>(tmQ, tmK, tmV, tmdO, p, stream);
   }
-  return bf16 ? launch_bwd_t<128, true>(tmQ, tmK, tmV, tmdO, p, stream)
-              : launch_bwd_t<128, false>(tmQ, tmK, tmV, tmdO, p, stream);
+  if (cap) {
+    return bf16 ? launch_bwd_t<128, true, true>(tmQ, tmK, tmV, tmdO, p, stream)
+                : launch_bwd_t<128, false, true>(tmQ, tmK, tmV, tmdO, p, stream);
+  }
+  return bf16 ? launch_bwd_t<128, true, false>(tmQ, tmK, tmV, tmdO, p, stream)
+              : launch_bwd_t<128, false, false>(tmQ, tmK, tmV, tmdO, p, stream);
 }
 
 }  // namespace omni

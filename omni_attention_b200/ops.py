@@ -38,6 +38,7 @@ ABI_SYMBOLS = (
     "omni_attn_build_mask_sm100",
     "omni_attn_bwd_workspace_bytes",
     "omni_attn_bwd_sm100",
+    "omni_attn_bwd_ex_sm100",
     "omni_attn_error_string",
     "omni_attn_last_cuda_error",
     "omni_attn_abi_version",
@@ -83,6 +84,8 @@ def load_library() -> ctypes.CDLL:
     lib.omni_attn_bwd_workspace_bytes.restype = ctypes.c_longlong
     lib.omni_attn_bwd_sm100.argtypes = [vp] * 15 + [i32] * 10 + [f32, vp, vp, vp, ctypes.c_longlong]
     lib.omni_attn_bwd_sm100.restype = i32
+    lib.omni_attn_bwd_ex_sm100.argtypes = lib.omni_attn_bwd_sm100.argtypes + [f32]
+    lib.omni_attn_bwd_ex_sm100.restype = i32
     lib.omni_attn_error_string.argtypes = [i32]
     lib.omni_attn_error_string.restype = ctypes.c_char_p
     lib.omni_attn_last_cuda_error.argtypes = []
@@ -324,10 +327,11 @@ def omni_attention(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBl
 def omni_attention_backward_out(q: Tensor, k: Tensor, v: Tensor, out: Tensor, lse: Tensor, d_out: Tensor,
                                 dq: Tensor, dk: Tensor, dv: Tensor, block_mask: OmniBlockMask, seqlen_orig: int,
                                 scale: Optional[float] = None, status: Optional[Tensor] = None,
-                                workspace: Optional[Tensor] = None) -> None:
+                                workspace: Optional[Tensor] = None, softcap: Optional[float] = None) -> None:
     """Launch the backward on padded, contiguous CUDA tensors; writes ``dq``, ``dk``, ``dv`` in place.
     ``out`` and ``lse`` are what the forward returned for the same inputs, mask and scale. The
-    reference has no backward; this is the gradient of its forward definition."""
+    reference has no backward; this is the gradient of its forward definition. ``softcap`` must be
+    the value the forward was run with."""
     tensors = (q, k, v, out, d_out, dq, dk, dv)
     if not all(t.is_cuda for t in tensors) or not lse.is_cuda:
         raise OmniAttnError("omni_attention backward needs CUDA tensors (there is no CPU path)")
@@ -346,13 +350,16 @@ def omni_attention_backward_out(q: Tensor, k: Tensor, v: Tensor, out: Tensor, ls
         workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
-        rc = lib.omni_attn_bwd_sm100(
-            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), d_out.data_ptr(),
-            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), m["nb"].data_ptr(), m["idx"].data_ptr(),
-            m["typ"].data_ptr(), _ptr(m["pidx"]), _ptr(m["pbool"]), _ptr(m["pbits"]), B, H, N, int(seqlen_orig), D,
-            block_mask.Q_BLOCK_SIZE, block_mask.KV_BLOCK_SIZE, int(m["idx"].shape[3]), m["num_partial"],
-            1 if q.dtype == torch.bfloat16 else 0, float(scale) if scale is not None else 0.0, stream,
-            _ptr(status), workspace.data_ptr(), workspace.numel() * workspace.element_size())
+        args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), d_out.data_ptr(),
+                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), m["nb"].data_ptr(), m["idx"].data_ptr(),
+                m["typ"].data_ptr(), _ptr(m["pidx"]), _ptr(m["pbool"]), _ptr(m["pbits"]), B, H, N, int(seqlen_orig), D,
+                block_mask.Q_BLOCK_SIZE, block_mask.KV_BLOCK_SIZE, int(m["idx"].shape[3]), m["num_partial"],
+                1 if q.dtype == torch.bfloat16 else 0, float(scale) if scale is not None else 0.0, stream,
+                _ptr(status), workspace.data_ptr(), workspace.numel() * workspace.element_size())
+        if softcap is not None and softcap > 0:
+            rc = lib.omni_attn_bwd_ex_sm100(*args, float(softcap))
+        else:
+            rc = lib.omni_attn_bwd_sm100(*args)
     _check(rc)
 
 
@@ -360,12 +367,12 @@ class _OmniAttentionFn(torch.autograd.Function):
     """Forward and backward kernels as one differentiable op on padded tensors."""
 
     @staticmethod
-    def forward(ctx, q, k, v, block_mask, seqlen_orig, scale):
+    def forward(ctx, q, k, v, block_mask, seqlen_orig, scale, softcap):
         out = torch.empty_like(q)
         lse = torch.empty(q.shape[0], q.shape[1], q.shape[2], dtype=torch.float32, device=q.device)
-        omni_attention_forward_out(q, k, v, out, block_mask, seqlen_orig, scale, lse)
+        omni_attention_forward_out(q, k, v, out, block_mask, seqlen_orig, scale, lse, softcap=softcap)
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.block_mask, ctx.seqlen_orig, ctx.scale = block_mask, seqlen_orig, scale
+        ctx.block_mask, ctx.seqlen_orig, ctx.scale, ctx.softcap = block_mask, seqlen_orig, scale, softcap
         return out
 
     @staticmethod
@@ -376,16 +383,17 @@ class _OmniAttentionFn(torch.autograd.Function):
             d_out = d_out.clone()
             d_out[:, :, ctx.seqlen_orig:] = 0   # padded rows take no part but must be finite
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        omni_attention_backward_out(q, k, v, out, lse, d_out, dq, dk, dv, ctx.block_mask, ctx.seqlen_orig, ctx.scale)
-        return dq, dk, dv, None, None, None
+        omni_attention_backward_out(q, k, v, out, lse, d_out, dq, dk, dv, ctx.block_mask, ctx.seqlen_orig, ctx.scale,
+                                    softcap=ctx.softcap)
+        return dq, dk, dv, None, None, None, None
 
 
 def omni_attention_autograd(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMask,
-                            scale: Optional[float] = None) -> Tensor:
+                            scale: Optional[float] = None, softcap: Optional[float] = None) -> Tensor:
     """``omni_attention`` for training: same inputs and output, differentiable with respect to
-    query, key and value (the gradients come from omni_attn_bwd_sm100)."""
+    query, key and value (the gradients come from omni_attn_bwd_sm100 / omni_attn_bwd_ex_sm100)."""
     qp, kp, vp, block_mask, scale, n_orig, d_orig = _prepare(query, key, value, block_mask, scale)
-    out = _OmniAttentionFn.apply(qp, kp, vp, block_mask, n_orig, scale)
+    out = _OmniAttentionFn.apply(qp, kp, vp, block_mask, n_orig, scale, softcap if softcap else None)
     return out[:, :, :n_orig, :d_orig]
 
 

@@ -16,7 +16,7 @@ import torch
 from torch import Tensor
 
 from .block_mask import OmniBlockMask, create_omni_block_mask_from_modality_positions
-from .ops import omni_attention
+from .ops import omni_attention, omni_attention_autograd
 
 
 def transfusion_block_mask(modality_positions: Tensor, heads: int, seq_len: int, device=None) -> OmniBlockMask:
@@ -33,4 +33,7 @@ def transfusion_attention_core(q: Tensor, k: Tensor, v: Tensor, block_mask: Omni
     """``out = softmax(mask(softcap * tanh(q k^T * scale / softcap))) v`` on [b, h, n, d] CUDA tensors
     (fp16 / bf16, d in {64, 128}); ``scale`` defaults to d ** -0.5 (:851) and ``softcap_value`` to the
     model's 50 (:844); 0 switches the soft-cap off as in the model (:958)."""
-    return omni_attention(q, k, v, block_mask, scale=scale, softcap=softcap_value if softcap_value > 0 else None)
+    cap = softcap_value if softcap_value > 0 else None
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return omni_attention_autograd(q, k, v, block_mask, scale=scale, softcap=cap)   # training: backward kernels
+    return omni_attention(q, k, v, block_mask, scale=scale, softcap=cap)

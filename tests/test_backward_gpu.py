@@ -165,3 +165,30 @@ def test_backward_rejects_a_small_workspace(cuda_device):
     ws = torch.empty(64, dtype=torch.uint8, device=cuda_device)
     with pytest.raises(ops.OmniAttnError, match="workspace"):
         ops.omni_attention_backward_out(q, q, q, q, lse, q, q.clone(), q.clone(), q.clone(), bm, 256, workspace=ws)
+
+
+@pytest.mark.parametrize("D,dtype", [(64, torch.float16), (128, torch.bfloat16)])
+def test_backward_with_softcap_through_the_transfusion_core(cuda_device, D, dtype):
+    """Training path of the Transfusion attention slot: soft-capped scores
+    (transfusion_pytorch/transfusion.py:298-299, :967) forward and backward. Scores are made large
+    enough for the cap to bend them."""
+    from omni_attention_b200.transfusion import transfusion_attention_core
+
+    torch.manual_seed(21)
+    n, cap = 512, 3.0
+    q, k, v, d_out = (torch.randn(1, 2, n, D).to(dtype) for _ in range(4))
+    q = (q.float() * 2.0).to(dtype)
+    bm = create_causal_omni_block_mask(1, 2, n, n)
+    bm.block_mask_types[:, :, 3, 1] = int(BlockMaskType.FULL)
+    qd, kd, vd = (t.to(cuda_device).requires_grad_(True) for t in (q, k, v))
+    out = transfusion_attention_core(qd, kd, vd, bm, softcap_value=cap)
+    assert out.requires_grad
+    out.backward(d_out.to(cuda_device))
+    ref_out, _ = orc.block_mask_attention(q, k, v, bm, softcap=cap)
+    assert float((out.detach().float().cpu() - ref_out).abs().max()) <= 2e-2 + 1e-2 * float(ref_out.abs().max())
+    ref = orc.block_mask_attention_backward(q, k, v, bm, d_out, softcap=cap)
+    got = tuple(t.grad.float().cpu() for t in (qd, kd, vd))
+    assert_grads(got, ref, dtype, [(0, 0), (0, 1)], "softcap")
+    # and the cap really matters for these inputs
+    plain = orc.block_mask_attention_backward(q, k, v, bm, d_out)
+    assert float((plain[0] - ref[0]).abs().max()) > 10 * GRAD_RTOL[dtype] * float(ref[0].abs().max())
