@@ -192,3 +192,26 @@ def test_backward_with_softcap_through_the_transfusion_core(cuda_device, D, dtyp
     # and the cap really matters for these inputs
     plain = orc.block_mask_attention_backward(q, k, v, bm, d_out)
     assert float((plain[0] - ref[0]).abs().max()) > 10 * GRAD_RTOL[dtype] * float(ref[0].abs().max())
+
+
+def test_backward_c5_shape_sampled_rows_and_columns(cuda_device):
+    """The 32K multi-image configuration: two of the 128 (batch, head) pairs on the GPU, one of them
+    checked at sampled query rows (dq) and key rows (dk, dv) against the block-at-a-time oracle, both
+    through properties that need no oracle."""
+    cfg = inputs.CONFIGS["C5"]
+    lo, hi = 48, 50
+    q, k, v, bm, _ = inputs.make_inputs("C5", seed=0, bh_range=(lo, hi))
+    torch.manual_seed(31)
+    d_out = (torch.randn(q.shape) * 0.5).to(q.dtype)
+    dq, dk, dv = backward(q, k, v, d_out, bm, cuda_device)
+    assert all(bool(torch.isfinite(t).all()) for t in (dq, dk, dv))
+    lhs, rhs = dv.sum(dim=2), d_out.float().sum(dim=2)
+    assert float((lhs - rhs).abs().max()) <= 2e-2 * float(rhs.abs().max()) + 1.0
+    g = torch.Generator().manual_seed(5)
+    rows = torch.randint(0, cfg.N, (48,), generator=g).tolist() + [0, 127, 128, cfg.N - 1, 4095, 4096]
+    cols = torch.randint(0, cfg.N, (48,), generator=g).tolist() + [0, 127, 128, cfg.N - 1, 20000, 20001]
+    rq, rk, rv = orc.blockwise_gradients(q, k, v, bm, d_out, 0, 1, rows, cols)
+    tol = GRAD_RTOL[q.dtype]
+    for name, got, ref in (("dq", dq[0, 1, rows], rq), ("dk", dk[0, 1, cols], rk), ("dv", dv[0, 1, cols], rv)):
+        err = float((got - ref).abs().max())
+        assert err <= tol * float(ref.abs().max()), f"C5 {name}: {err:.4g} vs max {float(ref.abs().max()):.4g}"
