@@ -6,7 +6,7 @@
 // failures raise std::runtime_error -> RuntimeError) and forwards to the C ABI of
 // libomni_attn_sm100.so. Differences from the reference, all supersets: bf16 is accepted as well
 // as fp16, the launch goes to torch's current stream instead of the legacy default stream, and
-// `omni_attn_fwd` adds optional scale / log-sum-exp / status arguments.
+// `omni_attn_fwd` adds optional scale / log-sum-exp / status arguments; `omni_attn_bwd` is the backward pass.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
@@ -179,6 +179,94 @@ void omni_attn_fwd(torch::Tensor Q, torch::Tensor K, torch::Tensor V, torch::Ten
                status, partial_bits);
 }
 
+// Backward pass on torch tensors (no counterpart in the reference's binding, which is forward-only):
+// the same mask arguments as the forward entry points, the forward's O and log-sum-exp, the gradient
+// of O, three output tensors and a caller-owned workspace of omni_attn_bwd_workspace_bytes(B, H, N)
+// bytes (the binding allocates nothing either).
+void omni_attn_bwd(torch::Tensor Q, torch::Tensor K, torch::Tensor V, torch::Tensor O, torch::Tensor lse,
+                   torch::Tensor dO, torch::Tensor dQ, torch::Tensor dK, torch::Tensor dV, torch::Tensor kv_num_blocks,
+                   torch::Tensor kv_indices, torch::Tensor block_mask_types, int Q_BLOCK_SIZE, int KV_BLOCK_SIZE,
+                   int seqlen_orig, torch::Tensor partial_block_mask_indices, torch::Tensor partial_block_masks,
+                   bool has_partial, torch::Tensor workspace, std::optional<double> scale,
+                   std::optional<torch::Tensor> status, std::optional<torch::Tensor> partial_bits, double softcap) {
+  const auto dtype = Q.scalar_type();
+  if (dtype != torch::kHalf && dtype != torch::kBFloat16) fail("Q must be torch.float16 or torch.bfloat16");
+  const torch::Tensor* same[] = {&Q, &K, &V, &O, &dO, &dQ, &dK, &dV};
+  const char* names[] = {"Q", "K", "V", "O", "dO", "dQ", "dK", "dV"};
+  for (int i = 0; i < 8; ++i) {
+    check_qkvo(*same[i], names[i], dtype);
+    if (same[i]->sizes() != Q.sizes()) fail(std::string(names[i]) + " must have the shape of Q");
+  }
+  const int B = static_cast<int>(Q.size(0)), H = static_cast<int>(Q.size(1));
+  const int N = static_cast<int>(Q.size(2)), D = static_cast<int>(Q.size(3));
+  if (!lse.is_cuda() || !lse.is_contiguous() || lse.scalar_type() != torch::kFloat32 ||
+      lse.numel() != static_cast<int64_t>(B) * H * N) {
+    fail("lse must be a contiguous CUDA float32 tensor [B, H, N]");
+  }
+  check_index(kv_num_blocks, "kv_num_blocks");
+  check_index(kv_indices, "kv_indices");
+  check_index(block_mask_types, "block_mask_types");
+  const int nq = (N + 127) / 128;
+  if (kv_num_blocks.dim() != 3 || kv_num_blocks.size(0) != B || kv_num_blocks.size(1) != H ||
+      kv_num_blocks.size(2) != nq || kv_indices.dim() != 4 || kv_indices.size(0) != B || kv_indices.size(1) != H ||
+      kv_indices.size(2) != nq || block_mask_types.sizes() != kv_indices.sizes()) {
+    fail("kv_num_blocks must be [B, H, num_q_blocks]; kv_indices and block_mask_types [B, H, num_q_blocks, max_blocks]");
+  }
+  const int32_t* pidx = nullptr;
+  const uint8_t* pbool = nullptr;
+  const uint32_t* pbits = nullptr;
+  int num_partial = 0;
+  if (has_partial) {
+    check_index(partial_block_mask_indices, "partial_block_mask_indices");
+    if (partial_block_mask_indices.sizes() != kv_indices.sizes()) {
+      fail("partial_block_mask_indices must have the shape of kv_indices");
+    }
+    if (!partial_block_masks.is_cuda() || !partial_block_masks.is_contiguous() ||
+        partial_block_masks.scalar_type() != torch::kBool) {
+      fail("partial_block_masks must be a contiguous CUDA torch.bool tensor");
+    }
+    num_partial = partial_block_masks.numel() > 0 ? static_cast<int>(partial_block_masks.size(0)) : 0;
+    pidx = partial_block_mask_indices.data_ptr<int32_t>();
+    if (num_partial > 0) pbool = reinterpret_cast<const uint8_t*>(partial_block_masks.data_ptr<bool>());
+    if (partial_bits.has_value() && num_partial > 0) {
+      const auto& pb = *partial_bits;
+      if (!pb.is_cuda() || !pb.is_contiguous() || pb.scalar_type() != torch::kInt32 ||
+          pb.numel() != static_cast<int64_t>(num_partial) * 128 * 4) {
+        fail("partial_bits must be a contiguous CUDA int32 tensor [num_partial, 128, 4]");
+      }
+      pbits = reinterpret_cast<const uint32_t*>(pb.data_ptr<int32_t>());
+    }
+  }
+  if (!workspace.is_cuda() || !workspace.is_contiguous()) fail("workspace must be a contiguous CUDA tensor");
+  int32_t* status_ptr = nullptr;
+  if (status.has_value()) {
+    const auto& st = *status;
+    if (!st.is_cuda() || st.scalar_type() != torch::kInt32 || st.numel() < 1) fail("status must be a CUDA int32 tensor");
+    status_ptr = st.data_ptr<int32_t>();
+  }
+  c10::cuda::CUDAGuard guard(Q.device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
+  const int rc = omni_attn_bwd_ex_sm100(
+      Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), lse.data_ptr<float>(), dO.data_ptr(), dQ.data_ptr(),
+      dK.data_ptr(), dV.data_ptr(), kv_num_blocks.data_ptr<int32_t>(), kv_indices.data_ptr<int32_t>(),
+      block_mask_types.data_ptr<int32_t>(), pidx, pbool, pbits, B, H, N, seqlen_orig, D, Q_BLOCK_SIZE, KV_BLOCK_SIZE,
+      static_cast<int>(kv_indices.size(3)), num_partial, dtype == torch::kBFloat16 ? OMNI_DTYPE_BF16 : OMNI_DTYPE_F16,
+      static_cast<float>(scale.value_or(0.0)), stream, status_ptr, workspace.data_ptr(),
+      static_cast<long long>(workspace.numel()) * static_cast<long long>(workspace.element_size()),
+      static_cast<float>(softcap));
+  if (rc != OMNI_OK) {
+    std::ostringstream os;
+    os << "omni_attn backward failed: " << omni_attn_error_string(rc) << " (code " << rc;
+    if (rc == OMNI_ERR_CUDA) os << ", CUDA error " << omni_attn_last_cuda_error();
+    os << ")";
+    fail(os.str());
+  }
+}
+
+long long omni_attn_bwd_workspace(int B, int H, int seqlen_padded) {
+  return omni_attn_bwd_workspace_bytes(B, H, seqlen_padded);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -197,4 +285,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("has_partial"), pybind11::arg("scale") = pybind11::none(),
         pybind11::arg("lse") = pybind11::none(), pybind11::arg("status") = pybind11::none(),
         pybind11::arg("partial_bits") = pybind11::none(), pybind11::arg("simple") = false);
+  m.def("omni_attn_bwd", &omni_attn_bwd, "backward: dQ, dK, dV from dO, the forward's O and log-sum-exp",
+        pybind11::arg("Q"), pybind11::arg("K"), pybind11::arg("V"), pybind11::arg("O"), pybind11::arg("lse"),
+        pybind11::arg("dO"), pybind11::arg("dQ"), pybind11::arg("dK"), pybind11::arg("dV"),
+        pybind11::arg("kv_num_blocks"), pybind11::arg("kv_indices"), pybind11::arg("block_mask_types"),
+        pybind11::arg("Q_BLOCK_SIZE"), pybind11::arg("KV_BLOCK_SIZE"), pybind11::arg("seqlen_orig"),
+        pybind11::arg("partial_block_mask_indices"), pybind11::arg("partial_block_masks"),
+        pybind11::arg("has_partial"), pybind11::arg("workspace"), pybind11::arg("scale") = pybind11::none(),
+        pybind11::arg("status") = pybind11::none(), pybind11::arg("partial_bits") = pybind11::none(),
+        pybind11::arg("softcap") = 0.0);
+  m.def("omni_attn_bwd_workspace_bytes", &omni_attn_bwd_workspace, "bytes of workspace omni_attn_bwd needs",
+        pybind11::arg("B"), pybind11::arg("H"), pybind11::arg("seqlen_padded"));
 }

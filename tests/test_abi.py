@@ -38,7 +38,8 @@ def test_pybind_module_exports_reference_names():
 
     m = pkg.install_reference_module()
     for n in ("omni_attn_mma_stages_split_q_shared_kv", "omni_attn_simple_kernel", "omni_attn_cp_async",
-              "omni_attn_preftech_kernel", "omni_attn_mma_stages_split_q_shared_kv_swizzle", "omni_attn_fwd"):
+              "omni_attn_preftech_kernel", "omni_attn_mma_stages_split_q_shared_kv_swizzle", "omni_attn_fwd",
+              "omni_attn_bwd", "omni_attn_bwd_workspace_bytes"):
         assert callable(getattr(m, n))
     # the reference's wrappers pass 13 positional arguments; anything else is a TypeError
     with pytest.raises(TypeError):

@@ -215,3 +215,29 @@ def test_backward_c5_shape_sampled_rows_and_columns(cuda_device):
     for name, got, ref in (("dq", dq[0, 1, rows], rq), ("dk", dk[0, 1, cols], rk), ("dv", dv[0, 1, cols], rv)):
         err = float((got - ref).abs().max())
         assert err <= tol * float(ref.abs().max()), f"C5 {name}: {err:.4g} vs max {float(ref.abs().max()):.4g}"
+
+
+def test_backward_through_the_pybind_module(cuda_device):
+    """`omni_attn.omni_attn_bwd` (torch tensors) gives the bits of the ctypes path."""
+    import omni_attention_b200 as pkg
+
+    m = pkg.install_reference_module()
+    g = load_golden("ref_fcp_n512_d64")
+    q, k, v, bm = (g[n].to(cuda_device) for n in ("q", "k", "v")) + (g["bm"],)
+    B, H, N, D = q.shape
+    torch.manual_seed(3)
+    d_out = torch.randn(q.shape).half().to(cuda_device)
+    dev = lambda t: t.to(cuda_device, torch.int32).contiguous()
+    nb, idx, typ, pidx = dev(bm.kv_num_blocks), dev(bm.kv_indices), dev(bm.block_mask_types), dev(bm.partial_block_mask_indices)
+    pool = bm.partial_block_masks.to(cuda_device).contiguous()
+    out = torch.empty_like(q)
+    lse = torch.empty(B, H, N, dtype=torch.float32, device=cuda_device)
+    m.omni_attn_fwd(q, k, v, out, nb, idx, typ, 128, 128, N, pidx, pool, True, lse=lse)
+    ws = torch.empty(m.omni_attn_bwd_workspace_bytes(B, H, N), dtype=torch.uint8, device=cuda_device)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    m.omni_attn_bwd(q, k, v, out, lse, d_out, dq, dk, dv, nb, idx, typ, 128, 128, N, pidx, pool, True, ws)
+    ref = backward(g["q"], g["k"], g["v"], d_out.cpu(), bm, cuda_device)
+    for a, b in zip((dq, dk, dv), ref):
+        assert torch.equal(a.float().cpu(), b)
+    with pytest.raises(RuntimeError, match="workspace"):
+        m.omni_attn_bwd(q, k, v, out, lse, d_out, dq, dk, dv, nb, idx, typ, 128, 128, N, pidx, pool, True, ws[:16])
