@@ -223,7 +223,8 @@ def test_backward_through_the_pybind_module(cuda_device):
 
     m = pkg.install_reference_module()
     g = load_golden("ref_fcp_n512_d64")
-    q, k, v, bm = (g[n].to(cuda_device) for n in ("q", "k", "v")) + (g["bm"],)
+    q, k, v = (g[n].half().to(cuda_device) for n in ("q", "k", "v"))
+    bm = g["bm"]
     B, H, N, D = q.shape
     torch.manual_seed(3)
     d_out = torch.randn(q.shape).half().to(cuda_device)
@@ -236,7 +237,7 @@ def test_backward_through_the_pybind_module(cuda_device):
     ws = torch.empty(m.omni_attn_bwd_workspace_bytes(B, H, N), dtype=torch.uint8, device=cuda_device)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
     m.omni_attn_bwd(q, k, v, out, lse, d_out, dq, dk, dv, nb, idx, typ, 128, 128, N, pidx, pool, True, ws)
-    ref = backward(g["q"], g["k"], g["v"], d_out.cpu(), bm, cuda_device)
+    ref = backward(g["q"].half(), g["k"].half(), g["v"].half(), d_out.cpu(), bm, cuda_device)
     for a, b in zip((dq, dk, dv), ref):
         assert torch.equal(a.float().cpu(), b)
     with pytest.raises(RuntimeError, match="workspace"):
