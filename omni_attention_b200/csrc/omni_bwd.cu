@@ -21,10 +21,12 @@
 //                             visited K, V stream; dQ += dS K with dS from TMEM.
 // S and dP are recomputed in both kernels (7 tile contractions per visited tile instead of 5), which
 // buys a deterministic result with no atomics and no fp32 dQ buffer.
-// Both kernels are plain: one CTA of 8 compute warps plus one warp whose first lane issues TMA and
-// tcgen05.mma (a lane that issues MMAs must not share its warp with lanes that spin on a barrier);
-// a tile row (= TMEM lane) is shared by two compute threads, one per warpgroup, each taking 64 of
-// its 128 columns. Loads are overlapped with compute; MMAs and the per-element work alternate.
+// Both tile kernels are warp-specialised: 8 compute warps (a tile row = TMEM lane is shared by two
+// threads, one per warpgroup, each taking 64 of its 128 columns), one warp whose first lane issues
+// every tcgen05.mma and one whose first lane issues the TMA loads; everything is handed over through
+// mbarriers (tcgen05.commit for "MMAs done", thread arrivals for "P / dS stored"). The per-element
+// work of a visit is split in two (probabilities from S; dS from dP and the probabilities) and the
+// MMAs of consecutive visits are interleaved so that the tensor pipe runs under both halves.
 #include <type_traits>
 
 #include "omni_common.cuh"
@@ -45,8 +47,9 @@ struct BwdCfg {
 };
 
 constexpr int kBwdComputeThreads = 256;
-constexpr int kBwdThreads = kBwdComputeThreads + 32;
-constexpr int kBwdIssuer = kBwdComputeThreads;   // thread that issues TMA and MMAs
+constexpr int kBwdThreads = kBwdComputeThreads + 64;
+constexpr int kBwdIssuer = kBwdComputeThreads;         // thread that issues the MMAs
+constexpr int kBwdProducer = kBwdComputeThreads + 32;  // thread that issues the TMA loads
 
 template <bool BF16>
 __device__ __forceinline__ float2 unpack2(uint32_t w) {
@@ -229,10 +232,23 @@ __device__ __forceinline__ float lse_to_log2(float lse) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// 2. dK, dV. One CTA per (KV block, batch*head), see bwd_decode_cta. Threads t and t + 128 own key row t of the block
-// (query columns [0,64) and [64,128)).
-// TMEM: two score regions [0,128) and [128,256) that S^T and dP^T swap between visits, dV
-// [256,256+D), dK [384,384+D). P^T and dS^T (16-bit) are written over S^T.
+// 2. dK, dV. One CTA per (KV block, batch*head), see bwd_decode_cta. 320 threads:
+//   warps 0-7  per-element work; threads t and t + 128 own key row t of the block (query columns
+//              [0,64) and [64,128) of the visited Q block)
+//   warp  8    first lane issues every tcgen05.mma
+//   warp  9    first lane issues the TMA loads
+// TMEM: two score regions R0 = [0,128), R1 = [128,256), dV [256,256+D), dK [384,384+D). Visit i puts
+// S^T in R(i&1) and dP^T in the other region; P^T and dS^T (16-bit) go over S^T, each thread writing
+// only columns it has read itself, so dP^T's region is dead as soon as dS^T is stored.
+//
+// The per-element work is split in two so that the tensor pipe always has something to do:
+//   E1(i): P^T  = exp2(S^T * c - LSE)        needs S^T(i)          -> feeds dV(i)
+//   E2(i): dS^T = P^T * (dP^T - delta)       needs dP^T(i), E1(i)  -> feeds dK(i)
+// and the MMAs of consecutive visits are interleaved in the order
+//   S^T(i), dK(i-1), dP^T(i), dV(i)
+// (S^T(i) overwrites dP^T(i-1), dead once E2(i-1) is done; dP^T(i) overwrites the region of visit
+// i-1 right after dK(i-1) has read dS^T(i-1) from it; E1(i) runs under dK(i-1) and dP^T(i), E2(i)
+// under dV(i)).
 // ---------------------------------------------------------------------------------------------
 template <int D, bool BF16, bool SOFTCAP>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -255,11 +271,16 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint16_t* vis_s = reinterpret_cast<uint16_t*>(code_s + kMaxKvBlocks);      // [kMaxKvBlocks]
   int* n_vis_s = reinterpret_cast<int*>(vis_s + kMaxKvBlocks);
   uint64_t* bars = reinterpret_cast<uint64_t*>(n_vis_s + 4);
-  const uint32_t bar_kv = smem_u32(bars + 0);
-  const uint32_t bar_ld = smem_u32(bars + 1);   // [2]
-  const uint32_t bar_s = smem_u32(bars + 3);
-  const uint32_t bar_acc = smem_u32(bars + 4);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  const uint32_t bar_kv = smem_u32(bars + 0);       // K, V landed
+  const uint32_t bar_q = smem_u32(bars + 1);        // [2] Q stage landed
+  const uint32_t bar_do = smem_u32(bars + 3);       // [2] dO stage landed
+  const uint32_t bar_s = smem_u32(bars + 5);        // S^T of the visit complete
+  const uint32_t bar_dp = smem_u32(bars + 6);       // dP^T of the visit complete
+  const uint32_t bar_p = smem_u32(bars + 7);        // P^T stored (256 arrivals)
+  const uint32_t bar_ds = smem_u32(bars + 8);       // dS^T stored (256 arrivals)
+  const uint32_t bar_dvdone = smem_u32(bars + 9);   // [2] dV MMAs of the visit in this stage complete: dO stage free
+  const uint32_t bar_dkdone = smem_u32(bars + 11);  // [2] dK MMAs complete: Q stage free
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x;
@@ -273,10 +294,16 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (tid == 0) {
     mbar_init(bar_kv, 1);
-    mbar_init(bar_ld, 1);
-    mbar_init(bar_ld + 8, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_q + 8 * s, 1);
+      mbar_init(bar_do + 8 * s, 1);
+      mbar_init(bar_dvdone + 8 * s, 1);
+      mbar_init(bar_dkdone + 8 * s, 1);
+    }
     mbar_init(bar_s, 1);
-    mbar_init(bar_acc, 1);
+    mbar_init(bar_dp, 1);
+    mbar_init(bar_p, kBwdComputeThreads);
+    mbar_init(bar_ds, kBwdComputeThreads);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -304,209 +331,214 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   // column kvb of this head's code table: which Q blocks visit this KV block, and how
   const int n_vis = bwd_build_visit_list(p.codes + static_cast<long long>(bh) * nq * nq + kvb, nq, nq, code_s, vis_s,
                                          n_vis_s);
-  auto visited_at = [&](int i, uint32_t& code) -> int {
-    if (i >= n_vis) {
-      code = 0u;
-      return nq;
-    }
-    const int qb = vis_s[i];
-    code = code_s[qb];
-    return qb;
+  auto stage_vectors = [&](int qb, int stage) {   // threads 0-127
+    const int q_abs = qb * kBlock + tid;
+    const long long row = row0 + q_abs;
+    const bool live = q_abs < p.f.seqlen_orig;
+    lse_s[stage * kBlock + tid] = live ? -lse_to_log2(__ldg(p.lse + row)) : -INFINITY;   // negated
+    delta_s[stage * kBlock + tid] = live ? -__ldg(p.delta + row) : 0.f;                   // negated
   };
-  // Staging of a Q block: the tiles (TMA, issuer thread) and the LSE / delta vectors (threads 0-127)
-  // become possible at different times, hence two pieces.
-  auto stage_tiles = [&](int qb, int stage) {
-    const uint32_t bar = bar_ld + 8 * stage;
-    mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
-    const int y = static_cast<int>(row0 + qb * kBlock);
-    bwd_load_tile<D>(sQ + stage * Cfg::kTileBytes, &tmQ, bar, y);
-    bwd_load_tile<D>(sdO + stage * Cfg::kTileBytes, &tmdO, bar, y);
-  };
-  auto stage_vectors = [&](int qb, int stage) {
-    if (tid < kBlock) {
-      const int q_abs = qb * kBlock + tid;
-      const long long row = row0 + q_abs;
-      const bool live = q_abs < p.f.seqlen_orig;
-      lse_s[stage * kBlock + tid] = live ? -lse_to_log2(__ldg(p.lse + row)) : -INFINITY;   // negated
-      delta_s[stage * kBlock + tid] = live ? -__ldg(p.delta + row) : 0.f;                   // negated
-    }
-  };
-  // Visit i keeps S^T in TMEM region (i & 1) and dP^T in the other one (128 columns each). The
-  // per-element pass writes P^T and dS^T over S^T only, so the dP^T region is free again as soon
-  // as that pass ends and takes the S^T of visit i + 1 while dV / dK of visit i are still running.
-  auto issue_scores = [&](int i) {   // issuer thread
-    const int stage = i & 1;
-    mbar_wait(bar_ld + 8 * stage, static_cast<uint32_t>((i >> 1) & 1), abort_flag, p.f.status, 51);
-    tc_fence_after();
-    bwd_mma_ss<D>(tmem_base + 128 * (i & 1), sK, sQ + stage * Cfg::kTileBytes, idesc_ss);            // S^T  = K Q^T
-    bwd_mma_ss<D>(tmem_base + 128 * ((i & 1) ^ 1), sV, sdO + stage * Cfg::kTileBytes, idesc_ss);    // dP^T = V dO^T
-    tc_commit(bar_s);
-  };
+  if (tid < kBlock) {
+    if (n_vis > 0) stage_vectors(vis_s[0], 0);
+    if (n_vis > 1) stage_vectors(vis_s[1], 1);
+  }
+  __syncthreads();   // the LSE / delta vectors are read by every compute thread
 
-  uint32_t code_cur = 0u, code_next = 0u;
-  int qb_cur = visited_at(0, code_cur);
-  if (n_vis > 0) {
-    uint32_t unused;
-    if (tid == kBwdIssuer) {
+  if (tid == kBwdProducer) {
+    // =========================== TMA producer ====================================================
+    if (n_vis > 0) {
       mbar_expect_tx(bar_kv, 2 * Cfg::kTileBytes);
       const int y = static_cast<int>(row0 + kvb * kBlock);
       bwd_load_tile<D>(sK, &tmK, bar_kv, y);
       bwd_load_tile<D>(sV, &tmV, bar_kv, y);
-      stage_tiles(qb_cur, 0);
-      if (n_vis > 1) stage_tiles(visited_at(1, unused), 1);
-      mbar_wait(bar_kv, 0, abort_flag, p.f.status, 50);
-      issue_scores(0);
     }
-    stage_vectors(qb_cur, 0);
-    if (n_vis > 1) stage_vectors(visited_at(1, unused), 1);
-  }
-  __syncthreads();   // the LSE / delta vectors are read by every thread
-  const int k_abs = kvb * kBlock + t;
-  const bool key_live = k_abs < p.f.seqlen_orig;
-  const float2 c2 = make_float2(p.f.scale_log2, p.f.scale_log2);
-
-  for (int it = 0; it < n_vis; ++it) {
-    const int stage = it & 1;
-    const uint32_t tS = tmem_base + 128 * (it & 1);          // S^T, then P^T / dS^T
-    const uint32_t tdP = tmem_base + 128 * ((it & 1) ^ 1);   // dP^T
-    const int qb_next = visited_at(it + 1, code_next);
-
-    // Allow-bits of this thread's key over its 64 query rows of the block (bit r of word w = query
-    // row 64 * half + 32 * w + r).
-    const uint32_t type = code_cur & kCodeTypeMask;
-    uint32_t allow[2] = {0xFFFFFFFFu, 0xFFFFFFFFu};
-    if (type == kTypePartial) {   // uniform over the CTA
-      if (tid < kBlock) {
-        uint32_t rowbits[4];
-        load_partial_row(p.f, code_cur >> 3, tid, rowbits);   // row tid of the tile = query row tid
-        *reinterpret_cast<uint4*>(bits_s + 4 * tid) = make_uint4(rowbits[0], rowbits[1], rowbits[2], rowbits[3]);
-      }
-      __syncthreads();
-#pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        uint32_t acc = 0u;
-#pragma unroll
-        for (int r = 0; r < 32; ++r) {
-          acc |= ((bits_s[4 * (64 * half + 32 * w + r) + (t >> 5)] >> (t & 31)) & 1u) << r;
-        }
-        allow[w] = acc;
-      }
-    } else if (type == kTypeCausal) {
-      // diagonal block: key t is seen by query rows r >= t
-#pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        const int d = t - 64 * half - 32 * w;   // lowest allowed bit in this word
-        allow[w] = d <= 0 ? 0xFFFFFFFFu : (d > 31 ? 0u : ~((1u << d) - 1u));
-      }
+    for (int i = 0; i < n_vis; ++i) {
+      const int stage = i & 1;
+      const int y = static_cast<int>(row0 + static_cast<int>(vis_s[i]) * kBlock);
+      const uint32_t prev = static_cast<uint32_t>(((i >> 1) - 1) & 1);   // parity of the stage's previous use
+      // Q first: it is needed first (S^T opens the visit) although its stage is freed last (by dK)
+      if (i >= 2) mbar_wait(bar_dkdone + 8 * stage, prev, abort_flag, p.f.status, 55);
+      mbar_expect_tx(bar_q + 8 * stage, Cfg::kTileBytes);
+      bwd_load_tile<D>(sQ + stage * Cfg::kTileBytes, &tmQ, bar_q + 8 * stage, y);
+      if (i >= 2) mbar_wait(bar_dvdone + 8 * stage, prev, abort_flag, p.f.status, 56);
+      mbar_expect_tx(bar_do + 8 * stage, Cfg::kTileBytes);
+      bwd_load_tile<D>(sdO + stage * Cfg::kTileBytes, &tmdO, bar_do + 8 * stage, y);
     }
-    if (!key_live) allow[0] = allow[1] = 0u;
-    const bool masked = type != kTypeFull || (code_cur & kCodeClip) || (qb_cur + 1) * kBlock > p.f.seqlen_orig;
-    const int q_live = p.f.seqlen_orig - qb_cur * kBlock - 64 * half;   // query rows [0, q_live) of this half exist
-    if (q_live < 64) {
-#pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        const int d = q_live - 1 - 32 * w;
-        allow[w] &= d >= 31 ? 0xFFFFFFFFu : (d < 0 ? 0u : ((2u << d) - 1u));
+  } else if (tid == kBwdIssuer) {
+    // =========================== MMA issuer ======================================================
+    for (int i = 0; i < n_vis; ++i) {
+      const int stage = i & 1;
+      const uint32_t ph = static_cast<uint32_t>(i & 1);
+      const uint32_t ld_ph = static_cast<uint32_t>((i >> 1) & 1);
+      const uint32_t tS = tmem_base + 128 * (i & 1);
+      const uint32_t tdP = tmem_base + 128 * ((i & 1) ^ 1);
+      if (i == 0) {
+        mbar_wait(bar_kv, 0, abort_flag, p.f.status, 50);
+      } else {
+        // E2 of the previous visit has read dP^T (its region takes this visit's S^T) and stored dS^T
+        mbar_wait(bar_ds, ph ^ 1u, abort_flag, p.f.status, 57);
       }
-    }
-
-    if (compute) {
-      mbar_wait_warp(bar_s, static_cast<uint32_t>(it & 1), abort_flag, p.f.status, 52);
+      mbar_wait(bar_q + 8 * stage, ld_ph, abort_flag, p.f.status, 51);
       tc_fence_after();
+      bwd_mma_ss<D>(tS, sK, sQ + stage * Cfg::kTileBytes, idesc_ss);                                  // S^T(i) = K Q^T
+      tc_commit(bar_s);
+      if (i > 0) {
+        bwd_mma_ts_split<D>(tdK, tdP, 32, sQ + (stage ^ 1) * Cfg::kTileBytes, idesc_ts, i > 1);      // dK += dS^T(i-1) Q(i-1)
+        tc_commit(bar_dkdone + 8 * (stage ^ 1));
+      }
+      mbar_wait(bar_do + 8 * stage, ld_ph, abort_flag, p.f.status, 52);
+      tc_fence_after();
+      bwd_mma_ss<D>(tdP, sV, sdO + stage * Cfg::kTileBytes, idesc_ss);                                // dP^T(i) = V dO^T
+      tc_commit(bar_dp);
+      mbar_wait(bar_p, ph, abort_flag, p.f.status, 58);
+      tc_fence_after();
+      bwd_mma_ts_split<D>(tdV, tS, 0, sdO + stage * Cfg::kTileBytes, idesc_ts, i > 0);               // dV += P^T(i) dO(i)
+      tc_commit(bar_dvdone + 8 * stage);
+    }
+    if (n_vis > 0) {
+      const int last = n_vis - 1;
+      mbar_wait(bar_ds, static_cast<uint32_t>(last & 1), abort_flag, p.f.status, 57);
+      tc_fence_after();
+      bwd_mma_ts_split<D>(tdK, tmem_base + 128 * (last & 1), 32, sQ + (last & 1) * Cfg::kTileBytes, idesc_ts, last > 0);
+      tc_commit(bar_dkdone + 8 * (last & 1));
+      // keep this thread alive until every MMA has retired
+      mbar_wait(bar_dkdone + 8 * (last & 1), static_cast<uint32_t>((last >> 1) & 1), abort_flag, p.f.status, 59);
+    }
+  } else if (compute) {
+    // =========================== per-element work ================================================
+    const int k_abs = kvb * kBlock + t;
+    const bool key_live = k_abs < p.f.seqlen_orig;
+    const float2 c2 = make_float2(p.f.scale_log2, p.f.scale_log2);
+    for (int i = 0; i < n_vis; ++i) {
+      const int stage = i & 1;
+      const uint32_t ph = static_cast<uint32_t>(i & 1);
+      const int qb = vis_s[i];
+      const uint32_t code = code_s[qb];
+      const uint32_t my_s = tmem_base + 128 * (i & 1) + lane_base + 64 * half;
+      const uint32_t my_dp = tmem_base + 128 * ((i & 1) ^ 1) + lane_base + 64 * half;
+
+      // Allow-bits of this thread's key over its 64 query rows of the block (bit r of word w = query
+      // row 64 * half + 32 * w + r).
+      const uint32_t type = code & kCodeTypeMask;
+      uint32_t allow[2] = {0xFFFFFFFFu, 0xFFFFFFFFu};
+      if (type == kTypePartial) {   // uniform over the compute threads
+        if (tid < kBlock) {
+          uint32_t rowbits[4];
+          load_partial_row(p.f, code >> 3, tid, rowbits);   // row tid of the tile = query row tid
+          *reinterpret_cast<uint4*>(bits_s + 4 * tid) = make_uint4(rowbits[0], rowbits[1], rowbits[2], rowbits[3]);
+        }
+        named_barrier_sync(1, kBwdComputeThreads);
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          uint32_t acc = 0u;
+#pragma unroll
+          for (int r = 0; r < 32; ++r) {
+            acc |= ((bits_s[4 * (64 * half + 32 * w + r) + (t >> 5)] >> (t & 31)) & 1u) << r;
+          }
+          allow[w] = acc;
+        }
+      } else if (type == kTypeCausal) {
+        // diagonal block: key t is seen by query rows r >= t
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          const int d = t - 64 * half - 32 * w;   // lowest allowed bit in this word
+          allow[w] = d <= 0 ? 0xFFFFFFFFu : (d > 31 ? 0u : ~((1u << d) - 1u));
+        }
+      }
+      if (!key_live) allow[0] = allow[1] = 0u;
+      const bool masked = type != kTypeFull || (code & kCodeClip) || (qb + 1) * kBlock > p.f.seqlen_orig;
+      const int q_live = p.f.seqlen_orig - qb * kBlock - 64 * half;   // query rows [0, q_live) of this half exist
+      if (q_live < 64) {
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          const int d = q_live - 1 - 32 * w;
+          allow[w] &= d >= 31 ? 0xFFFFFFFFu : (d < 0 ? 0u : ((2u << d) - 1u));
+        }
+      }
+
+      // ---- E1: P^T -------------------------------------------------------------------------------
       const float* lse_c = lse_s + stage * kBlock + 64 * half;
       const float* del_c = delta_s + stage * kBlock + 64 * half;
-      const uint32_t my_s = tS + lane_base + 64 * half;
-      const uint32_t my_dp = tdP + lane_base + 64 * half;
-      uint32_t dd0[16];
-      // two copies of the loop, so that tiles without any masking (the bulk) carry no select at all
-      auto tile_math = [&](auto masked_c) {
+      float pf[64];      // the unrounded probabilities (times the soft-cap slope, if any), kept for E2
+      mbar_wait_warp(bar_s, ph, abort_flag, p.f.status, 52);
+      tc_fence_after();
+      auto e1 = [&](auto masked_c) {
         constexpr bool kMasked = decltype(masked_c)::value;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t rs[32], rd[32];
+          uint32_t rs[32];
           tmem_ld32(my_s + 32 * c, rs);
-          tmem_ld32(my_dp + 32 * c, rd);
           tc_wait_ld();
-          uint32_t pp[16], dd[16];
+          uint32_t pp[16];
           const uint32_t aw = allow[c];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float2 nl = *reinterpret_cast<const float2*>(lse_c + 32 * c + 2 * j);
-            const float2 nd = *reinterpret_cast<const float2*>(del_c + 32 * c + 2 * j);
             float2 sc = make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1]));
-            float2 slope;
+            float2 slope = make_float2(1.f, 1.f);
             if constexpr (SOFTCAP) slope = bwd_soft_cap(sc, p.f.cap_in, p.f.cap_out);
             const float2 x = __ffma2_rn(sc, c2, nl);
             float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-            float2 ds = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd));
-            if constexpr (SOFTCAP) ds = __fmul2_rn(ds, slope);
             if constexpr (kMasked) {
-              const bool ok0 = (aw >> (2 * j)) & 1u, ok1 = (aw >> (2 * j + 1)) & 1u;
-              pr.x = ok0 ? pr.x : 0.f;
-              pr.y = ok1 ? pr.y : 0.f;
-              ds.x = ok0 ? ds.x : 0.f;
-              ds.y = ok1 ? ds.y : 0.f;
+              pr.x = ((aw >> (2 * j)) & 1u) ? pr.x : 0.f;
+              pr.y = ((aw >> (2 * j + 1)) & 1u) ? pr.y : 0.f;
             }
             pp[j] = pack2<BF16>(pr.x, pr.y);
-            dd[j] = pack2<BF16>(ds.x, ds.y);
+            if constexpr (SOFTCAP) pr = __fmul2_rn(pr, slope);
+            pf[32 * c + 2 * j] = pr.x;
+            pf[32 * c + 2 * j + 1] = pr.y;
           }
-          // P^T over this thread's S^T columns [0,32) of its half, dS^T over [32,64): chunk c has
-          // been read completely (chunk 0 covers [0,32)), and nobody else touches these columns
+          // P^T over this thread's S^T columns [0,32) of its half: chunk 0 has been read completely
           tmem_st16(my_s + 16 * c, pp);
-          if (c == 1) {
-            tmem_st16(my_s + 32, dd0);
-            tmem_st16(my_s + 48, dd);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) dd0[j] = dd[j];
-          }
         }
       };
-      if (masked) {   // uniform over the CTA
-        tile_math(std::true_type{});
+      if (masked) {   // uniform over the compute threads
+        e1(std::true_type{});
       } else {
-        tile_math(std::false_type{});
+        e1(std::false_type{});
       }
       tc_wait_st();
-    }
-    tc_fence_before();
-    __syncthreads();
+      tc_fence_before();
+      mbar_arrive(bar_p);
 
-    if (tid == kBwdIssuer) {
+      // ---- E2: dS^T ------------------------------------------------------------------------------
+      mbar_wait_warp(bar_dp, ph, abort_flag, p.f.status, 53);
       tc_fence_after();
-      bwd_mma_ts_split<D>(tdV, tS, 0, sdO + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dV += P^T dO
-      bwd_mma_ts_split<D>(tdK, tS, 32, sQ + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dK += dS^T Q
-      tc_commit(bar_acc);
-      if (it + 1 < n_vis) issue_scores(it + 1);
-      if (it + 2 < n_vis) {
-        // the tiles of this visit are free once its dV / dK MMAs have completed
-        mbar_wait(bar_acc, static_cast<uint32_t>(it & 1), abort_flag, p.f.status, 53);
-        uint32_t unused;
-        stage_tiles(visited_at(it + 2, unused), stage);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rd[32];
+        tmem_ld32(my_dp + 32 * c, rd);
+        tc_wait_ld();
+        uint32_t dd[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 nd = *reinterpret_cast<const float2*>(del_c + 32 * c + 2 * j);
+          const float2 ds = __fmul2_rn(make_float2(pf[32 * c + 2 * j], pf[32 * c + 2 * j + 1]),
+                                       __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd));
+          dd[j] = pack2<BF16>(ds.x, ds.y);
+        }
+        // dS^T over this thread's S^T columns [32,64) of its half (read in E1)
+        tmem_st16(my_s + 32 + 16 * c, dd);
       }
-    }
-    if (it + 2 < n_vis) {
-      uint32_t unused;
-      stage_vectors(visited_at(it + 2, unused), stage);   // read two barriers from here
-    }
-    qb_cur = qb_next;
-    code_cur = code_next;
-  }
-  const int it = n_vis;
-  if (n_vis > 0) {
-    if (compute) {
-      mbar_wait_warp(bar_acc, static_cast<uint32_t>((n_vis - 1) & 1), abort_flag, p.f.status, 54);
-    } else if (tid == kBwdIssuer) {
-      mbar_wait(bar_acc, static_cast<uint32_t>((n_vis - 1) & 1), abort_flag, p.f.status, 54);
-    }
-    tc_fence_after();
-  }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_ds);
 
-  const long long out_row = row0 + k_abs;
-  if (compute && half == 0) {
-    bwd_store_row<D, BF16>(tdV + lane_base, it > 0, 1.f, p.dv, out_row);
-  } else if (compute) {
-    bwd_store_row<D, BF16>(tdK + lane_base, it > 0, p.f.scale, p.dk, out_row);
+      // the vectors of this stage are free once every compute thread is through E2
+      named_barrier_sync(2, kBwdComputeThreads);
+      if (tid < kBlock && i + 2 < n_vis) stage_vectors(vis_s[i + 2], stage);
+    }
+    if (n_vis > 0) {
+      const int last = n_vis - 1;
+      mbar_wait_warp(bar_dkdone + 8 * (last & 1), static_cast<uint32_t>((last >> 1) & 1), abort_flag, p.f.status, 54);
+      tc_fence_after();
+    }
+    const long long out_row = row0 + k_abs;
+    if (half == 0) {
+      bwd_store_row<D, BF16>(tdV + lane_base, n_vis > 0, 1.f, p.dv, out_row);
+    } else {
+      bwd_store_row<D, BF16>(tdK + lane_base, n_vis > 0, p.f.scale, p.dk, out_row);
+    }
   }
 
   tc_fence_before();
@@ -515,34 +547,54 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 }
 
 // ---------------------------------------------------------------------------------------------
-// 3. dQ. One CTA per (Q block, batch*head), see bwd_decode_cta. Threads t and t + 128 own query row t of the block
-// (key columns [0,64) and [64,128)).
-// TMEM: two score regions [0,128) and [128,256) that S and dP swap between visits, dQ [256,256+D).
-// dS (16-bit) is written over S.
+// 3. dQ. One CTA per (Q block, batch*head), see bwd_decode_cta. Same roles as the dK/dV kernel
+// (threads t and t + 128 own query row t, key columns [0,64) and [64,128) of the visited KV block).
+// TMEM: three score regions R0, R1, R2 = [0,128), [128,256), [256,384), dQ [384,384+D). Visit i puts
+// S in A(i) = R(2i mod 3) and dP in B(i) = R((2i+1) mod 3); dS (16-bit) goes over S. The third
+// region is what lets the scores run ahead: A(i+2) = B(i) is dead once E2(i) is done, B(i+1) = A(i)
+// once dQ(i) has read dS(i), so the tensor pipe works in the order
+//   dQ(i), dP(i+1), S(i+2)
+// while the compute warps do E1(i+1) (probabilities, kept in registers) under dQ(i) / dP(i+1) and
+// E2(i+1) (dS) under S(i+2). K is needed by S two visits ahead and by dQ, hence a ring of three K
+// tiles (two for V); with Q and dO resident that is all of an SM's shared memory at D=128, so the
+// buffer is declared 1024-byte aligned instead of being aligned by hand.
 // ---------------------------------------------------------------------------------------------
+template <int D>
+struct DqCfg {
+  static constexpr int kTileBytes = kBlock * D * 2;
+  static constexpr int kListBytes = kMaxKvBlocks * 2 + 16;   // visit list, its length
+  static constexpr int kSmemBytes = 7 * kTileBytes + kListBytes + 256;
+};
+
 template <int D, bool BF16, bool SOFTCAP>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const BwdParams p) {
-  using Cfg = BwdCfg<D>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  uint8_t* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  using Cfg = DqCfg<D>;
+  extern __shared__ __align__(1024) uint8_t smem_dq[];
+  uint8_t* smem = smem_dq;
+  if ((smem_u32(smem) & 1023u) != 0u) {   // the swizzled tile layout needs it; uniform over the CTA
+    if (threadIdx.x == 0 && p.f.status != nullptr) atomicExch(p.f.status, kStatusWaitTimeout | (69 << 8));
+    return;
+  }
 
   const uint32_t sQ = smem_u32(smem);
   const uint32_t sdO = sQ + Cfg::kTileBytes;
-  const uint32_t sK = sdO + Cfg::kTileBytes;           // two stages
-  const uint32_t sV = sK + 2 * Cfg::kTileBytes;        // two stages
-  uint32_t* code_s = reinterpret_cast<uint32_t*>(smem + 6 * Cfg::kTileBytes);   // [kMaxKvBlocks]
-  uint16_t* vis_s = reinterpret_cast<uint16_t*>(code_s + kMaxKvBlocks);          // [kMaxKvBlocks]
+  const uint32_t sK = sdO + Cfg::kTileBytes;           // three stages
+  const uint32_t sV = sK + 3 * Cfg::kTileBytes;        // two stages
+  uint16_t* vis_s = reinterpret_cast<uint16_t*>(smem + 7 * Cfg::kTileBytes);   // [kMaxKvBlocks]
   int* n_vis_s = reinterpret_cast<int*>(vis_s + kMaxKvBlocks);
   uint64_t* bars = reinterpret_cast<uint64_t*>(n_vis_s + 4);
-  const uint32_t bar_q = smem_u32(bars + 0);
-  const uint32_t bar_ld = smem_u32(bars + 1);   // [2]
-  const uint32_t bar_s = smem_u32(bars + 3);
-  const uint32_t bar_acc = smem_u32(bars + 4);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  const uint32_t bar_qdo = smem_u32(bars + 0);     // Q, dO landed
+  const uint32_t bar_k = smem_u32(bars + 1);       // [3] K stage landed
+  const uint32_t bar_v = smem_u32(bars + 4);       // [2] V stage landed
+  const uint32_t bar_s = smem_u32(bars + 6);       // [2] S of a visit complete (by visit parity)
+  const uint32_t bar_dp = smem_u32(bars + 8);      // dP of the visit complete
+  const uint32_t bar_ds = smem_u32(bars + 9);      // dS stored (256 arrivals)
+  const uint32_t bar_kfree = smem_u32(bars + 10);  // [3] dQ MMAs that read this K stage complete
+  const uint32_t bar_vfree = smem_u32(bars + 13);  // [2] dP MMAs that read this V stage complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x;
@@ -555,11 +607,18 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   bwd_decode_cta(p.f, static_cast<int>(blockIdx.x), true, qb, bh);
 
   if (tid == 0) {
-    mbar_init(bar_q, 1);
-    mbar_init(bar_ld, 1);
-    mbar_init(bar_ld + 8, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_acc, 1);
+    mbar_init(bar_qdo, 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(bar_k + 8 * s, 1);
+      mbar_init(bar_kfree + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_v + 8 * s, 1);
+      mbar_init(bar_vfree + 8 * s, 1);
+      mbar_init(bar_s + 8 * s, 1);
+    }
+    mbar_init(bar_dp, 1);
+    mbar_init(bar_ds, kBwdComputeThreads);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -568,7 +627,7 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tma_prefetch_desc(&tmdO);
   }
   if (warp == 0) {
-    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -577,153 +636,173 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  const uint32_t tdQ = tmem_base + 256;
+  const uint32_t tdQ = tmem_base + 384;
+  auto region_s = [&](int i) { return tmem_base + 128u * static_cast<uint32_t>((2 * i) % 3); };
+  auto region_dp = [&](int i) { return tmem_base + 128u * static_cast<uint32_t>((2 * i + 1) % 3); };
   constexpr int fmt = BF16 ? 1 : 0;
   constexpr uint32_t idesc_ss = umma_idesc_f16(128, 128, fmt, 0);
   constexpr uint32_t idesc_ts = umma_idesc_f16(128, D, fmt, 1);
 
   const long long row0 = static_cast<long long>(bh) * p.f.N;
   // row qb of this head's code table: the KV blocks this Q block visits, and how
-  const int n_vis = bwd_build_visit_list(p.codes + (static_cast<long long>(bh) * nq + qb) * nq, 1, nq, code_s, vis_s,
-                                         n_vis_s);
-  auto visited_at = [&](int i, uint32_t& code) -> int {
-    if (i >= n_vis) {
-      code = 0u;
-      return nq;
+  const uint32_t* codes_row = p.codes + (static_cast<long long>(bh) * nq + qb) * nq;
+  if (warp == 0) {
+    const int lane = tid;
+    int count = 0;
+    for (int base = 0; base < nq; base += 32) {
+      const bool on = base + lane < nq && __ldg(codes_row + base + lane) != 0u;
+      const uint32_t any = __ballot_sync(0xFFFFFFFFu, on);
+      if (on) vis_s[count + __popc(any & ((1u << lane) - 1u))] = static_cast<uint16_t>(base + lane);
+      count += __popc(any);
     }
-    const int kvb = vis_s[i];
-    code = code_s[kvb];
-    return kvb;
-  };
-  auto stage_tiles = [&](int kvb, int stage) {   // issuer thread
-    const uint32_t bar = bar_ld + 8 * stage;
-    mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
-    const int y = static_cast<int>(row0 + kvb * kBlock);
-    bwd_load_tile<D>(sK + stage * Cfg::kTileBytes, &tmK, bar, y);
-    bwd_load_tile<D>(sV + stage * Cfg::kTileBytes, &tmV, bar, y);
-  };
-  // Visit i keeps S in TMEM region (i & 1) and dP in the other one; dS is written over S, so the dP
-  // region takes the S of visit i + 1 while dQ of visit i is still running.
-  auto issue_scores = [&](int i) {   // issuer thread
-    const int stage = i & 1;
-    mbar_wait(bar_ld + 8 * stage, static_cast<uint32_t>((i >> 1) & 1), abort_flag, p.f.status, 61);
-    tc_fence_after();
-    bwd_mma_ss<D>(tmem_base + 128 * (i & 1), sQ, sK + stage * Cfg::kTileBytes, idesc_ss);            // S  = Q K^T
-    bwd_mma_ss<D>(tmem_base + 128 * ((i & 1) ^ 1), sdO, sV + stage * Cfg::kTileBytes, idesc_ss);    // dP = dO V^T
-    tc_commit(bar_s);
-  };
-
-  const int q_abs = qb * kBlock + t;
-  const long long my_row = row0 + q_abs;
-  const bool q_live = q_abs < p.f.seqlen_orig;
-  // a row beyond the sequence (or one that attended nothing) gets -LSE = -inf: every probability 0
-  const float neg_lse2 = q_live ? -lse_to_log2(__ldg(p.lse + my_row)) : -INFINITY;
-  const float neg_delta = q_live ? -__ldg(p.delta + my_row) : 0.f;
-  const float2 c2 = make_float2(p.f.scale_log2, p.f.scale_log2);
-  const float2 nl2 = make_float2(neg_lse2, neg_lse2);
-  const float2 nd2 = make_float2(neg_delta, neg_delta);
-
-  uint32_t code_cur = 0u, code_next = 0u;
-  int kvb_cur = visited_at(0, code_cur);
-  if (n_vis > 0 && tid == kBwdIssuer) {
-    uint32_t unused;
-    mbar_expect_tx(bar_q, 2 * Cfg::kTileBytes);
-    const int y = static_cast<int>(row0 + qb * kBlock);
-    bwd_load_tile<D>(sQ, &tmQ, bar_q, y);
-    bwd_load_tile<D>(sdO, &tmdO, bar_q, y);
-    stage_tiles(kvb_cur, 0);
-    if (n_vis > 1) stage_tiles(visited_at(1, unused), 1);
-    mbar_wait(bar_q, 0, abort_flag, p.f.status, 60);
-    issue_scores(0);
+    if (lane == 0) *n_vis_s = count;
   }
+  __syncthreads();
+  const int n_vis = *n_vis_s;
 
-  for (int it = 0; it < n_vis; ++it) {
-    const int stage = it & 1;
-    const uint32_t tS = tmem_base + 128 * (it & 1);          // S, then dS
-    const uint32_t tdP = tmem_base + 128 * ((it & 1) ^ 1);   // dP
-    const int kvb_next = visited_at(it + 1, code_next);
-
-    const bool masked = (code_cur & kCodeTypeMask) != kTypeFull || (code_cur & kCodeClip);
-    uint32_t allow[4] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
-    if (masked) build_allow(p.f, code_cur, kvb_cur, t, allow);
-
-    if (compute) {
-      mbar_wait_warp(bar_s, static_cast<uint32_t>(it & 1), abort_flag, p.f.status, 62);
+  if (tid == kBwdProducer) {
+    // =========================== TMA producer ====================================================
+    if (n_vis > 0) {
+      mbar_expect_tx(bar_qdo, 2 * Cfg::kTileBytes);
+      const int y = static_cast<int>(row0 + qb * kBlock);
+      bwd_load_tile<D>(sQ, &tmQ, bar_qdo, y);
+      bwd_load_tile<D>(sdO, &tmdO, bar_qdo, y);
+    }
+    for (int j = 0; j < n_vis; ++j) {
+      const int y = static_cast<int>(row0 + static_cast<int>(vis_s[j]) * kBlock);
+      const int ks = j % 3, vs = j & 1;
+      if (j >= 3) mbar_wait(bar_kfree + 8 * ks, static_cast<uint32_t>((j / 3 - 1) & 1), abort_flag, p.f.status, 65);
+      mbar_expect_tx(bar_k + 8 * ks, Cfg::kTileBytes);
+      bwd_load_tile<D>(sK + ks * Cfg::kTileBytes, &tmK, bar_k + 8 * ks, y);
+      if (j >= 2) mbar_wait(bar_vfree + 8 * vs, static_cast<uint32_t>(((j >> 1) - 1) & 1), abort_flag, p.f.status, 66);
+      mbar_expect_tx(bar_v + 8 * vs, Cfg::kTileBytes);
+      bwd_load_tile<D>(sV + vs * Cfg::kTileBytes, &tmV, bar_v + 8 * vs, y);
+    }
+  } else if (tid == kBwdIssuer) {
+    // =========================== MMA issuer ======================================================
+    auto issue_s = [&](int j) {    // S(j) = Q K(j)^T
+      mbar_wait(bar_k + 8 * (j % 3), static_cast<uint32_t>((j / 3) & 1), abort_flag, p.f.status, 61);
       tc_fence_after();
-      const uint32_t my_s = tS + lane_base + 64 * half;
-      const uint32_t my_dp = tdP + lane_base + 64 * half;
-      auto tile_math = [&](auto masked_c) {
+      bwd_mma_ss<D>(region_s(j), sQ, sK + (j % 3) * Cfg::kTileBytes, idesc_ss);
+      tc_commit(bar_s + 8 * (j & 1));
+    };
+    auto issue_dp = [&](int j) {   // dP(j) = dO V(j)^T
+      mbar_wait(bar_v + 8 * (j & 1), static_cast<uint32_t>((j >> 1) & 1), abort_flag, p.f.status, 62);
+      tc_fence_after();
+      bwd_mma_ss<D>(region_dp(j), sdO, sV + (j & 1) * Cfg::kTileBytes, idesc_ss);
+      tc_commit(bar_dp);
+      tc_commit(bar_vfree + 8 * (j & 1));
+    };
+    if (n_vis > 0) {
+      mbar_wait(bar_qdo, 0, abort_flag, p.f.status, 60);
+      issue_s(0);
+      issue_dp(0);
+      if (n_vis > 1) issue_s(1);
+    }
+    for (int i = 0; i < n_vis; ++i) {
+      mbar_wait(bar_ds, static_cast<uint32_t>(i & 1), abort_flag, p.f.status, 63);
+      tc_fence_after();
+      bwd_mma_ts_split<D>(tdQ, region_s(i), 0, sK + (i % 3) * Cfg::kTileBytes, idesc_ts, i > 0);   // dQ += dS(i) K(i)
+      tc_commit(bar_kfree + 8 * (i % 3));
+      if (i + 1 < n_vis) issue_dp(i + 1);
+      if (i + 2 < n_vis) issue_s(i + 2);
+    }
+    if (n_vis > 0) {
+      const int last = n_vis - 1;
+      mbar_wait(bar_kfree + 8 * (last % 3), static_cast<uint32_t>((last / 3) & 1), abort_flag, p.f.status, 64);
+    }
+  } else if (compute) {
+    // =========================== per-element work ================================================
+    const int q_abs = qb * kBlock + t;
+    const long long my_row = row0 + q_abs;
+    const bool q_live = q_abs < p.f.seqlen_orig;
+    // a row beyond the sequence (or one that attended nothing) gets -LSE = -inf: every probability 0
+    const float neg_lse2 = q_live ? -lse_to_log2(__ldg(p.lse + my_row)) : -INFINITY;
+    const float neg_delta = q_live ? -__ldg(p.delta + my_row) : 0.f;
+    const float2 c2 = make_float2(p.f.scale_log2, p.f.scale_log2);
+    const float2 nl2 = make_float2(neg_lse2, neg_lse2);
+    const float2 nd2 = make_float2(neg_delta, neg_delta);
+
+    for (int i = 0; i < n_vis; ++i) {
+      const int kvb = vis_s[i];
+      const uint32_t code = __ldg(codes_row + kvb);
+      const uint32_t my_s = region_s(i) + lane_base + 64 * half;
+      const uint32_t my_dp = region_dp(i) + lane_base + 64 * half;
+      const bool masked = (code & kCodeTypeMask) != kTypeFull || (code & kCodeClip);
+      uint32_t allow[4] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
+      if (masked) build_allow(p.f, code, kvb, t, allow);
+
+      // ---- E1: probabilities (times the soft-cap slope, if any), kept in registers ---------------
+      float pf[64];
+      mbar_wait_warp(bar_s + 8 * (i & 1), static_cast<uint32_t>((i >> 1) & 1), abort_flag, p.f.status, 67);
+      tc_fence_after();
+      auto e1 = [&](auto masked_c) {
         constexpr bool kMasked = decltype(masked_c)::value;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t rs[32], rd[32];
+          uint32_t rs[32];
           tmem_ld32(my_s + 32 * c, rs);
-          tmem_ld32(my_dp + 32 * c, rd);
           tc_wait_ld();
-          uint32_t dd[16];
           const uint32_t aw = allow[2 * half + c];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             float2 sc = make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1]));
-            float2 slope;
+            float2 slope = make_float2(1.f, 1.f);
             if constexpr (SOFTCAP) slope = bwd_soft_cap(sc, p.f.cap_in, p.f.cap_out);
             const float2 x = __ffma2_rn(sc, c2, nl2);
-            const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-            float2 ds = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd2));
-            if constexpr (SOFTCAP) ds = __fmul2_rn(ds, slope);
+            float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+            if constexpr (SOFTCAP) pr = __fmul2_rn(pr, slope);
             if constexpr (kMasked) {
-              ds.x = ((aw >> (2 * j)) & 1u) ? ds.x : 0.f;
-              ds.y = ((aw >> (2 * j + 1)) & 1u) ? ds.y : 0.f;
+              pr.x = ((aw >> (2 * j)) & 1u) ? pr.x : 0.f;
+              pr.y = ((aw >> (2 * j + 1)) & 1u) ? pr.y : 0.f;
             }
-            dd[j] = pack2<BF16>(ds.x, ds.y);
+            pf[32 * c + 2 * j] = pr.x;
+            pf[32 * c + 2 * j + 1] = pr.y;
           }
-          // dS over this thread's S columns [0,32) of its half: columns it has read already
-          tmem_st16(my_s + 16 * c, dd);
         }
       };
-      if (masked) {   // uniform over the CTA
-        tile_math(std::true_type{});
+      if (masked) {   // uniform over the compute threads
+        e1(std::true_type{});
       } else {
-        tile_math(std::false_type{});
+        e1(std::false_type{});
+      }
+
+      // ---- E2: dS over this thread's S columns [0,32) of its half ---------------------------------
+      mbar_wait_warp(bar_dp, static_cast<uint32_t>(i & 1), abort_flag, p.f.status, 68);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rd[32];
+        tmem_ld32(my_dp + 32 * c, rd);
+        tc_wait_ld();
+        uint32_t dd[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 ds = __fmul2_rn(make_float2(pf[32 * c + 2 * j], pf[32 * c + 2 * j + 1]),
+                                       __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd2));
+          dd[j] = pack2<BF16>(ds.x, ds.y);
+        }
+        tmem_st16(my_s + 16 * c, dd);
       }
       tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_ds);
     }
-    tc_fence_before();
-    __syncthreads();
-
-    if (tid == kBwdIssuer) {
+    if (n_vis > 0) {
+      const int last = n_vis - 1;
+      mbar_wait_warp(bar_kfree + 8 * (last % 3), static_cast<uint32_t>((last / 3) & 1), abort_flag, p.f.status, 64);
       tc_fence_after();
-      bwd_mma_ts_split<D>(tdQ, tS, 0, sK + stage * Cfg::kTileBytes, idesc_ts, it > 0);   // dQ += dS K
-      tc_commit(bar_acc);
-      if (it + 1 < n_vis) issue_scores(it + 1);
-      if (it + 2 < n_vis) {
-        mbar_wait(bar_acc, static_cast<uint32_t>(it & 1), abort_flag, p.f.status, 63);
-        uint32_t unused;
-        stage_tiles(visited_at(it + 2, unused), stage);
-      }
     }
-    kvb_cur = kvb_next;
-    code_cur = code_next;
-  }
-  const int it = n_vis;
-  if (n_vis > 0) {
-    if (compute) {
-      mbar_wait_warp(bar_acc, static_cast<uint32_t>((n_vis - 1) & 1), abort_flag, p.f.status, 64);
-    } else if (tid == kBwdIssuer) {
-      mbar_wait(bar_acc, static_cast<uint32_t>((n_vis - 1) & 1), abort_flag, p.f.status, 64);
+    if (half == 0) {
+      bwd_store_row<D, BF16, 0, D / 64>(tdQ + lane_base, n_vis > 0, p.f.scale, p.dq, my_row);
+    } else {
+      bwd_store_row<D, BF16, D / 64, D / 32>(tdQ + lane_base, n_vis > 0, p.f.scale, p.dq, my_row);
     }
-    tc_fence_after();
-  }
-
-  if (compute && half == 0) {
-    bwd_store_row<D, BF16, 0, D / 64>(tdQ + lane_base, it > 0, p.f.scale, p.dq, my_row);
-  } else if (compute) {
-    bwd_store_row<D, BF16, D / 64, D / 32>(tdQ + lane_base, it > 0, p.f.scale, p.dq, my_row);
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  if (warp == 0) tmem_dealloc(tmem_base, 512);
 }
 
 template <int D, bool BF16, bool SOFTCAP>
@@ -736,7 +815,7 @@ static cudaError_t launch_bwd_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, 
   static bool attr_dq[64] = {};
   cudaError_t e = ensure_smem_attr(dkdv, Cfg::kSmemBytes, attr_dkdv);
   if (e != cudaSuccess) return e;
-  e = ensure_smem_attr(dq, Cfg::kSmemBytes, attr_dq);
+  e = ensure_smem_attr(dq, DqCfg<D>::kSmemBytes, attr_dq);
   if (e != cudaSuccess) return e;
   const dim3 grid(p.f.nq, p.f.BH);
   omni_bwd_prep_kernel<D, BF16><<<grid, 128, 0, stream>>>(p);
@@ -746,7 +825,7 @@ static cudaError_t launch_bwd_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, 
   dkdv<<<ctas, kBwdThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmK, tmV, tmdO, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  dq<<<ctas, kBwdThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmK, tmV, tmdO, p);
+  dq<<<ctas, kBwdThreads, DqCfg<D>::kSmemBytes, stream>>>(tmQ, tmK, tmV, tmdO, p);
   return cudaGetLastError();
 }
 
