@@ -50,6 +50,20 @@ constexpr int kBwdComputeThreads = 256;
 constexpr int kBwdThreads = kBwdComputeThreads + 64;
 constexpr int kBwdIssuer = kBwdComputeThreads;         // thread that issues the MMAs
 constexpr int kBwdProducer = kBwdComputeThreads + 32;  // thread that issues the TMA loads
+constexpr bool kBwdDkFirst = false;
+
+// Profiling build (-DOMNI_BWD_PROFILE): the MMA-issuing thread adds up the cycles it spends in each
+// of its waits into 64-bit counters behind the status word (slot + 16 for the dQ kernel).
+#ifdef OMNI_BWD_PROFILE
+#define OMNI_BWD_TIMED(slot, call)                                                              \
+  do {                                                                                          \
+    const long long t_begin_ = clock64();                                                       \
+    call;                                                                                       \
+    prof_acc[slot] += clock64() - t_begin_;                                                     \
+  } while (0)
+#else
+#define OMNI_BWD_TIMED(slot, call) call
+#endif
 
 template <bool BF16>
 __device__ __forceinline__ float2 unpack2(uint32_t w) {
@@ -366,6 +380,10 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
   } else if (tid == kBwdIssuer) {
     // =========================== MMA issuer ======================================================
+#ifdef OMNI_BWD_PROFILE
+    long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long prof_t0 = clock64();
+#endif
     for (int i = 0; i < n_vis; ++i) {
       const int stage = i & 1;
       const uint32_t ph = static_cast<uint32_t>(i & 1);
@@ -376,21 +394,26 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         mbar_wait(bar_kv, 0, abort_flag, p.f.status, 50);
       } else {
         // E2 of the previous visit has read dP^T (its region takes this visit's S^T) and stored dS^T
-        mbar_wait(bar_ds, ph ^ 1u, abort_flag, p.f.status, 57);
+        OMNI_BWD_TIMED(0, mbar_wait(bar_ds, ph ^ 1u, abort_flag, p.f.status, 57));
       }
-      mbar_wait(bar_q + 8 * stage, ld_ph, abort_flag, p.f.status, 51);
-      tc_fence_after();
-      bwd_mma_ss<D>(tS, sK, sQ + stage * Cfg::kTileBytes, idesc_ss);                                  // S^T(i) = K Q^T
-      tc_commit(bar_s);
-      if (i > 0) {
+      if (kBwdDkFirst && i > 0) {
+        tc_fence_after();
         bwd_mma_ts_split<D>(tdK, tdP, 32, sQ + (stage ^ 1) * Cfg::kTileBytes, idesc_ts, i > 1);      // dK += dS^T(i-1) Q(i-1)
         tc_commit(bar_dkdone + 8 * (stage ^ 1));
       }
-      mbar_wait(bar_do + 8 * stage, ld_ph, abort_flag, p.f.status, 52);
+      OMNI_BWD_TIMED(1, mbar_wait(bar_q + 8 * stage, ld_ph, abort_flag, p.f.status, 51));
+      tc_fence_after();
+      bwd_mma_ss<D>(tS, sK, sQ + stage * Cfg::kTileBytes, idesc_ss);                                  // S^T(i) = K Q^T
+      tc_commit(bar_s);
+      if (!kBwdDkFirst && i > 0) {
+        bwd_mma_ts_split<D>(tdK, tdP, 32, sQ + (stage ^ 1) * Cfg::kTileBytes, idesc_ts, i > 1);      // dK += dS^T(i-1) Q(i-1)
+        tc_commit(bar_dkdone + 8 * (stage ^ 1));
+      }
+      OMNI_BWD_TIMED(2, mbar_wait(bar_do + 8 * stage, ld_ph, abort_flag, p.f.status, 52));
       tc_fence_after();
       bwd_mma_ss<D>(tdP, sV, sdO + stage * Cfg::kTileBytes, idesc_ss);                                // dP^T(i) = V dO^T
       tc_commit(bar_dp);
-      mbar_wait(bar_p, ph, abort_flag, p.f.status, 58);
+      OMNI_BWD_TIMED(3, mbar_wait(bar_p, ph, abort_flag, p.f.status, 58));
       tc_fence_after();
       bwd_mma_ts_split<D>(tdV, tS, 0, sdO + stage * Cfg::kTileBytes, idesc_ts, i > 0);               // dV += P^T(i) dO(i)
       tc_commit(bar_dvdone + 8 * stage);
@@ -404,6 +427,14 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // keep this thread alive until every MMA has retired
       mbar_wait(bar_dkdone + 8 * (last & 1), static_cast<uint32_t>((last >> 1) & 1), abort_flag, p.f.status, 59);
     }
+#ifdef OMNI_BWD_PROFILE
+    if (p.f.status != nullptr) {
+      unsigned long long* prof = reinterpret_cast<unsigned long long*>(p.f.status + 4);
+      for (int j = 0; j < 4; ++j) atomicAdd(prof + j, static_cast<unsigned long long>(prof_acc[j]));
+      atomicAdd(prof + 4, static_cast<unsigned long long>(clock64() - prof_t0));
+      atomicAdd(prof + 5, static_cast<unsigned long long>(n_vis));
+    }
+#endif
   } else if (compute) {
     // =========================== per-element work ================================================
     const int k_abs = kvb * kBlock + t;
@@ -680,14 +711,18 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else if (tid == kBwdIssuer) {
     // =========================== MMA issuer ======================================================
+#ifdef OMNI_BWD_PROFILE
+    long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long prof_t0 = clock64();
+#endif
     auto issue_s = [&](int j) {    // S(j) = Q K(j)^T
-      mbar_wait(bar_k + 8 * (j % 3), static_cast<uint32_t>((j / 3) & 1), abort_flag, p.f.status, 61);
+      OMNI_BWD_TIMED(1, mbar_wait(bar_k + 8 * (j % 3), static_cast<uint32_t>((j / 3) & 1), abort_flag, p.f.status, 61));
       tc_fence_after();
       bwd_mma_ss<D>(region_s(j), sQ, sK + (j % 3) * Cfg::kTileBytes, idesc_ss);
       tc_commit(bar_s + 8 * (j & 1));
     };
     auto issue_dp = [&](int j) {   // dP(j) = dO V(j)^T
-      mbar_wait(bar_v + 8 * (j & 1), static_cast<uint32_t>((j >> 1) & 1), abort_flag, p.f.status, 62);
+      OMNI_BWD_TIMED(2, mbar_wait(bar_v + 8 * (j & 1), static_cast<uint32_t>((j >> 1) & 1), abort_flag, p.f.status, 62));
       tc_fence_after();
       bwd_mma_ss<D>(region_dp(j), sdO, sV + (j & 1) * Cfg::kTileBytes, idesc_ss);
       tc_commit(bar_dp);
@@ -700,7 +735,7 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (n_vis > 1) issue_s(1);
     }
     for (int i = 0; i < n_vis; ++i) {
-      mbar_wait(bar_ds, static_cast<uint32_t>(i & 1), abort_flag, p.f.status, 63);
+      OMNI_BWD_TIMED(0, mbar_wait(bar_ds, static_cast<uint32_t>(i & 1), abort_flag, p.f.status, 63));
       tc_fence_after();
       bwd_mma_ts_split<D>(tdQ, region_s(i), 0, sK + (i % 3) * Cfg::kTileBytes, idesc_ts, i > 0);   // dQ += dS(i) K(i)
       tc_commit(bar_kfree + 8 * (i % 3));
@@ -711,6 +746,14 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int last = n_vis - 1;
       mbar_wait(bar_kfree + 8 * (last % 3), static_cast<uint32_t>((last / 3) & 1), abort_flag, p.f.status, 64);
     }
+#ifdef OMNI_BWD_PROFILE
+    if (p.f.status != nullptr) {
+      unsigned long long* prof = reinterpret_cast<unsigned long long*>(p.f.status + 4) + 16;
+      for (int j = 0; j < 4; ++j) atomicAdd(prof + j, static_cast<unsigned long long>(prof_acc[j]));
+      atomicAdd(prof + 4, static_cast<unsigned long long>(clock64() - prof_t0));
+      atomicAdd(prof + 5, static_cast<unsigned long long>(n_vis));
+    }
+#endif
   } else if (compute) {
     // =========================== per-element work ================================================
     const int q_abs = qb * kBlock + t;
