@@ -278,8 +278,9 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t sV = sK + Cfg::kTileBytes;
   const uint32_t sQ = sV + Cfg::kTileBytes;            // two stages
   const uint32_t sdO = sQ + 2 * Cfg::kTileBytes;       // two stages
-  float* lse_s = reinterpret_cast<float*>(smem + 6 * Cfg::kTileBytes);   // [2][128], -LSE in the log2 domain
-  float* delta_s = lse_s + 2 * kBlock;                                    // [2][128], -delta
+  // LSE (+inf for a dead row) and delta of the visited Q block as loaded, two stages
+  float* lse_s = reinterpret_cast<float*>(smem + 6 * Cfg::kTileBytes);   // [2][128]
+  float* delta_s = lse_s + 2 * kBlock;                                    // [2][128]
   uint32_t* bits_s = reinterpret_cast<uint32_t*>(delta_s + 2 * kBlock);   // [128][4]
   uint32_t* code_s = bits_s + kBlock * 4;                                   // [kMaxKvBlocks]
   uint16_t* vis_s = reinterpret_cast<uint16_t*>(code_s + kMaxKvBlocks);      // [kMaxKvBlocks]
@@ -349,8 +350,9 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int q_abs = qb * kBlock + tid;
     const long long row = row0 + q_abs;
     const bool live = q_abs < p.f.seqlen_orig;
-    lse_s[stage * kBlock + tid] = live ? -lse_to_log2(__ldg(p.lse + row)) : -INFINITY;   // negated
-    delta_s[stage * kBlock + tid] = live ? -__ldg(p.delta + row) : 0.f;                   // negated
+    const float l = live ? __ldg(p.lse + row) : INFINITY;
+    lse_s[stage * kBlock + tid] = l == -INFINITY ? INFINITY : l;   // a row that attended nothing is dead too
+    delta_s[stage * kBlock + tid] = live ? __ldg(p.delta + row) : 0.f;
   };
   if (tid < kBlock) {
     if (n_vis > 0) stage_vectors(vis_s[0], 0);
@@ -440,13 +442,31 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int k_abs = kvb * kBlock + t;
     const bool key_live = k_abs < p.f.seqlen_orig;
     const float2 c2 = make_float2(p.f.scale_log2, p.f.scale_log2);
+#ifdef OMNI_BWD_PROFILE
+    long long cprof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long ct = clock64();
+#define OMNI_CSTAMP(j) if (tid == 0) { const long long now_ = clock64(); cprof[j] += now_ - ct; ct = now_; }
+#else
+#define OMNI_CSTAMP(j)
+#endif
     for (int i = 0; i < n_vis; ++i) {
+      OMNI_CSTAMP(0);
       const int stage = i & 1;
       const uint32_t ph = static_cast<uint32_t>(i & 1);
       const int qb = vis_s[i];
       const uint32_t code = code_s[qb];
       const uint32_t my_s = tmem_base + 128 * (i & 1) + lane_base + 64 * half;
       const uint32_t my_dp = tmem_base + 128 * ((i & 1) ^ 1) + lane_base + 64 * half;
+      // LSE / delta of the visit after next: the global loads are issued here and land in shared
+      // memory at the end of this visit (stored as loaded), so their latency is off everybody's path
+      float next_lse = INFINITY, next_delta = 0.f;
+      if (tid < kBlock && i + 2 < n_vis) {
+        const int q_abs = static_cast<int>(vis_s[i + 2]) * kBlock + tid;
+        if (q_abs < p.f.seqlen_orig) {
+          next_lse = __ldg(p.lse + row0 + q_abs);
+          next_delta = __ldg(p.delta + row0 + q_abs);
+        }
+      }
 
       // Allow-bits of this thread's key over its 64 query rows of the block (bit r of word w = query
       // row 64 * half + 32 * w + r).
@@ -491,20 +511,25 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const float* lse_c = lse_s + stage * kBlock + 64 * half;
       const float* del_c = delta_s + stage * kBlock + 64 * half;
       float pf[64];      // the unrounded probabilities (times the soft-cap slope, if any), kept for E2
+      OMNI_CSTAMP(1);
       mbar_wait_warp(bar_s, ph, abort_flag, p.f.status, 52);
       tc_fence_after();
+      OMNI_CSTAMP(2);
       auto e1 = [&](auto masked_c) {
         constexpr bool kMasked = decltype(masked_c)::value;
+        uint32_t rs2[2][32];
+        tmem_ld32(my_s, rs2[0]);
+        tmem_ld32(my_s + 32, rs2[1]);
+        tc_wait_ld();
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t rs[32];
-          tmem_ld32(my_s + 32 * c, rs);
-          tc_wait_ld();
+          const uint32_t (&rs)[32] = rs2[c];
           uint32_t pp[16];
           const uint32_t aw = allow[c];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float2 nl = *reinterpret_cast<const float2*>(lse_c + 32 * c + 2 * j);
+            const float2 nl = __fmul2_rn(*reinterpret_cast<const float2*>(lse_c + 32 * c + 2 * j),
+                                         make_float2(-1.4426950408889634f, -1.4426950408889634f));   // +inf (dead row) -> -inf
             float2 sc = make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1]));
             float2 slope = make_float2(1.f, 1.f);
             if constexpr (SOFTCAP) slope = bwd_soft_cap(sc, p.f.cap_in, p.f.cap_out);
@@ -531,21 +556,26 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p);
+      OMNI_CSTAMP(3);
 
       // ---- E2: dS^T ------------------------------------------------------------------------------
       mbar_wait_warp(bar_dp, ph, abort_flag, p.f.status, 53);
       tc_fence_after();
+      OMNI_CSTAMP(4);
+      uint32_t rd2[2][32];
+      tmem_ld32(my_dp, rd2[0]);
+      tmem_ld32(my_dp + 32, rd2[1]);
+      tc_wait_ld();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t rd[32];
-        tmem_ld32(my_dp + 32 * c, rd);
-        tc_wait_ld();
+        const uint32_t (&rd)[32] = rd2[c];
         uint32_t dd[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const float2 nd = *reinterpret_cast<const float2*>(del_c + 32 * c + 2 * j);
+          const float2 dl = *reinterpret_cast<const float2*>(del_c + 32 * c + 2 * j);
           const float2 ds = __fmul2_rn(make_float2(pf[32 * c + 2 * j], pf[32 * c + 2 * j + 1]),
-                                       __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])), nd));
+                                       __fadd2_rn(make_float2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1])),
+                                                  make_float2(-dl.x, -dl.y)));
           dd[j] = pack2<BF16>(ds.x, ds.y);
         }
         // dS^T over this thread's S^T columns [32,64) of its half (read in E1)
@@ -554,11 +584,23 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_ds);
+      OMNI_CSTAMP(5);
 
-      // the vectors of this stage are free once every compute thread is through E2
+      // the vectors (and the partial-mask bits) of this visit are free once every compute thread is
+      // through E2
       named_barrier_sync(2, kBwdComputeThreads);
-      if (tid < kBlock && i + 2 < n_vis) stage_vectors(vis_s[i + 2], stage);
+      if (tid < kBlock && i + 2 < n_vis) {
+        lse_s[stage * kBlock + tid] = next_lse == -INFINITY ? INFINITY : next_lse;
+        delta_s[stage * kBlock + tid] = next_delta;
+      }
+      OMNI_CSTAMP(6);
     }
+#ifdef OMNI_BWD_PROFILE
+    if (tid == 0 && p.f.status != nullptr) {
+      unsigned long long* prof = reinterpret_cast<unsigned long long*>(p.f.status + 4) + 32;
+      for (int j = 0; j < 7; ++j) atomicAdd(prof + j, static_cast<unsigned long long>(cprof[j]));
+    }
+#endif
     if (n_vis > 0) {
       const int last = n_vis - 1;
       mbar_wait_warp(bar_dkdone + 8 * (last & 1), static_cast<uint32_t>((last >> 1) & 1), abort_flag, p.f.status, 54);
@@ -581,12 +623,12 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 // 3. dQ. One CTA per (Q block, batch*head), see bwd_decode_cta. Same roles as the dK/dV kernel
 // (threads t and t + 128 own query row t, key columns [0,64) and [64,128) of the visited KV block).
 // TMEM: three score regions R0, R1, R2 = [0,128), [128,256), [256,384), dQ [384,384+D). Visit i puts
-// S in A(i) = R(2i mod 3) and dP in B(i) = R((2i+1) mod 3); dS (16-bit) goes over S. The third
-// region is what lets the scores run ahead: A(i+2) = B(i) is dead once E2(i) is done, B(i+1) = A(i)
-// once dQ(i) has read dS(i), so the tensor pipe works in the order
-//   dQ(i), dP(i+1), S(i+2)
-// while the compute warps do E1(i+1) (probabilities, kept in registers) under dQ(i) / dP(i+1) and
-// E2(i+1) (dS) under S(i+2). K is needed by S two visits ahead and by dQ, hence a ring of three K
+// S in R(i&1) and dP in R2; dS (16-bit) goes over S. The third region is what lets the scores run
+// ahead: R2 is dead once E2(i) is done and takes dP(i+1) at once, R(i&1) is free once dQ(i) has read
+// dS(i) and takes S(i+2), so the tensor pipe works in the order
+//   dP(i+1), dQ(i), S(i+2)
+// while the compute warps do E1(i+1) (probabilities, kept in registers) under dP(i+1) and E2(i+1)
+// (dS) under dQ(i) / S(i+2). K is needed by S two visits ahead and by dQ, hence a ring of three K
 // tiles (two for V); with Q and dO resident that is all of an SM's shared memory at D=128, so the
 // buffer is declared 1024-byte aligned instead of being aligned by hand.
 // ---------------------------------------------------------------------------------------------
@@ -668,8 +710,8 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   const uint32_t tdQ = tmem_base + 384;
-  auto region_s = [&](int i) { return tmem_base + 128u * static_cast<uint32_t>((2 * i) % 3); };
-  auto region_dp = [&](int i) { return tmem_base + 128u * static_cast<uint32_t>((2 * i + 1) % 3); };
+  auto region_s = [&](int i) { return tmem_base + 128u * static_cast<uint32_t>(i & 1); };
+  auto region_dp = [&](int) { return tmem_base + 256u; };
   constexpr int fmt = BF16 ? 1 : 0;
   constexpr uint32_t idesc_ss = umma_idesc_f16(128, 128, fmt, 0);
   constexpr uint32_t idesc_ts = umma_idesc_f16(128, D, fmt, 1);
@@ -737,9 +779,9 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < n_vis; ++i) {
       OMNI_BWD_TIMED(0, mbar_wait(bar_ds, static_cast<uint32_t>(i & 1), abort_flag, p.f.status, 63));
       tc_fence_after();
+      if (i + 1 < n_vis) issue_dp(i + 1);   // first: E2(i+1) is waiting for it
       bwd_mma_ts_split<D>(tdQ, region_s(i), 0, sK + (i % 3) * Cfg::kTileBytes, idesc_ts, i > 0);   // dQ += dS(i) K(i)
       tc_commit(bar_kfree + 8 * (i % 3));
-      if (i + 1 < n_vis) issue_dp(i + 1);
       if (i + 2 < n_vis) issue_s(i + 2);
     }
     if (n_vis > 0) {
@@ -781,11 +823,13 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       auto e1 = [&](auto masked_c) {
         constexpr bool kMasked = decltype(masked_c)::value;
+        uint32_t rs2[2][32];
+        tmem_ld32(my_s, rs2[0]);
+        tmem_ld32(my_s + 32, rs2[1]);
+        tc_wait_ld();
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t rs[32];
-          tmem_ld32(my_s + 32 * c, rs);
-          tc_wait_ld();
+          const uint32_t (&rs)[32] = rs2[c];
           const uint32_t aw = allow[2 * half + c];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -813,11 +857,13 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // ---- E2: dS over this thread's S columns [0,32) of its half ---------------------------------
       mbar_wait_warp(bar_dp, static_cast<uint32_t>(i & 1), abort_flag, p.f.status, 68);
       tc_fence_after();
+      uint32_t rd2[2][32];
+      tmem_ld32(my_dp, rd2[0]);
+      tmem_ld32(my_dp + 32, rd2[1]);
+      tc_wait_ld();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t rd[32];
-        tmem_ld32(my_dp + 32 * c, rd);
-        tc_wait_ld();
+        const uint32_t (&rd)[32] = rd2[c];
         uint32_t dd[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {

@@ -82,28 +82,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-// Warp-collective wait: lane 0 polls (with a short back-off between polls), the other lanes park at
-// the warp barrier. 32 lanes polling the same mbarrier cost shared-memory bandwidth and issue slots
-// that the tensor pipe's operand reads and the MMA-issuing thread need. All 32 lanes must call it.
+// Warp-collective wait: lane 0 polls, the other lanes park at the warp barrier. 32 lanes polling the
+// same mbarrier cost shared-memory bandwidth and issue slots that the tensor pipe's operand reads and
+// the MMA-issuing thread need; a sleep between polls, on the other hand, was measured to wake the
+// warp hundreds of cycles late. All 32 lanes must call it.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                int32_t* status, int where) {
   bool ok = true;
-  if ((threadIdx.x & 31) == 0) {
-    ok = mbar_try_wait(bar, parity) != 0;
-    if (!ok && !*abort_flag) {
-      const long long t0 = clock64();
-      while (true) {
-        __nanosleep(32);
-        if (mbar_try_wait(bar, parity)) { ok = true; break; }
-        if (*abort_flag) break;
-        if (clock64() - t0 > kWaitCycleLimit) {
-          *abort_flag = 1;
-          if (status != nullptr) atomicExch(status, kStatusWaitTimeout | (where << 8));
-          break;
-        }
-      }
-    }
-  }
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status, where);
   __syncwarp();
   return ok;
 }
