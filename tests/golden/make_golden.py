@@ -84,4 +84,6 @@ def main(ref_dir: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference/omni-attn-mma")
+    here = os.path.dirname(os.path.abspath(__file__))
+    default = os.path.normpath(os.path.join(here, "..", "..", "..", "reference", "omni-attn-mma"))
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("OMNI_REFERENCE_DIR", default))

@@ -13,7 +13,9 @@ from omni_attention_b200.block_mask import (BlockMaskType, OmniBlockMask, block_
                                             row_limits_from_modality_positions)
 from oracle import omni_oracle as orc
 
-REF_DIR = os.environ.get("OMNI_REFERENCE_DIR", "/root/reference/omni-attn-mma")
+# the reference checkout, when there is one: next to this repository unless OMNI_REFERENCE_DIR says otherwise
+REF_DIR = os.environ.get("OMNI_REFERENCE_DIR") or os.path.normpath(
+    os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference", "omni-attn-mma"))
 
 
 def test_type_codes_match_reference_enum():

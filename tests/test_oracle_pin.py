@@ -12,7 +12,9 @@ from conftest import GOLDEN_CASES, load_golden
 from oracle import omni_oracle as orc
 from oracle import scalar
 
-REF_DIR = os.environ.get("OMNI_REFERENCE_DIR", "/root/reference/omni-attn-mma")
+# the reference checkout, when there is one: next to this repository unless OMNI_REFERENCE_DIR says otherwise
+REF_DIR = os.environ.get("OMNI_REFERENCE_DIR") or os.path.normpath(
+    os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference", "omni-attn-mma"))
 
 
 @pytest.mark.parametrize("name", GOLDEN_CASES)
