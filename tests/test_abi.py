@@ -108,3 +108,44 @@ def test_operator_refuses_cpu_tensors():
     bm.KV_BLOCK_SIZE = 32
     with pytest.raises(ValueError):
         omni_attention(q, q, q, bm)
+
+
+def _call_bwd(lib, fn="omni_attn_bwd_sm100", **kw):
+    buf = (ctypes.c_char * 4096)()
+    a = (ctypes.addressof(buf) + 15) & ~15
+    d = dict(q=a, k=a, v=a, o=a, lse=a, do=a, dq=a, dk=a, dv=a, nb=a, idx=a, typ=a, pidx=None, pbool=None, pbits=None,
+             B=1, H=1, N=128, orig=128, D=64, qb=128, kb=128, mb=1, npart=0, dtype=0, scale=0.0, stream=None, status=None,
+             ws=a, ws_bytes=1 << 20)
+    d.update(kw)
+    args = [d["q"], d["k"], d["v"], d["o"], d["lse"], d["do"], d["dq"], d["dk"], d["dv"], d["nb"], d["idx"], d["typ"],
+            d["pidx"], d["pbool"], d["pbits"], d["B"], d["H"], d["N"], d["orig"], d["D"], d["qb"], d["kb"], d["mb"],
+            d["npart"], d["dtype"], d["scale"], d["stream"], d["status"], d["ws"], d["ws_bytes"]]
+    if fn == "omni_attn_bwd_ex_sm100":
+        args.append(d.get("softcap", 0.0))
+    return getattr(lib, fn)(*args)
+
+
+@pytest.mark.parametrize("fn", ["omni_attn_bwd_sm100", "omni_attn_bwd_ex_sm100"])
+def test_backward_argument_validation_codes(fn):
+    """The backward entry points check their arguments before anything touches the device."""
+    lib = ops.load_library()
+    E = error_codes()
+    for name in ("q", "lse", "do", "dq", "dk", "dv", "typ", "ws"):
+        assert _call_bwd(lib, fn, **{name: None}) == E["OMNI_ERR_NULL_POINTER"], name
+    assert _call_bwd(lib, fn, dtype=3) == E["OMNI_ERR_DTYPE"]
+    assert _call_bwd(lib, fn, D=32) == E["OMNI_ERR_HEAD_DIM"]
+    assert _call_bwd(lib, fn, qb=64, kb=64) == E["OMNI_ERR_BLOCK_SIZE"]
+    assert _call_bwd(lib, fn, N=130) == E["OMNI_ERR_SEQLEN"]
+    assert _call_bwd(lib, fn, orig=200) == E["OMNI_ERR_SEQLEN"]
+    assert _call_bwd(lib, fn, H=0) == E["OMNI_ERR_SHAPE"]
+    assert _call_bwd(lib, fn, npart=2) == E["OMNI_ERR_PARTIAL"]
+    assert _call_bwd(lib, fn, N=128 * 1025, orig=128) == E["OMNI_ERR_TOO_LONG"]
+    assert _call_bwd(lib, fn, ws_bytes=16) == E["OMNI_ERR_WORKSPACE"]
+    base = (ctypes.addressof((ctypes.c_char * 64)()) + 15) & ~15
+    assert _call_bwd(lib, fn, dq=base + 4) == E["OMNI_ERR_ALIGNMENT"]
+    if fn == "omni_attn_bwd_ex_sm100":
+        assert _call_bwd(lib, fn, softcap=-1.0) == E["OMNI_ERR_SOFTCAP"]
+        assert _call_bwd(lib, fn, softcap=float("nan")) == E["OMNI_ERR_SOFTCAP"]
+    # the workspace size the header promises: codes [BH, nq, nq] rounded to 256 bytes + delta [BH, N]
+    assert lib.omni_attn_bwd_workspace_bytes(2, 3, 512) == ((6 * 4 * 4 * 4 + 255) // 256) * 256 + 6 * 512 * 4
+    assert lib.omni_attn_bwd_workspace_bytes(2, 3, 500) == 0
