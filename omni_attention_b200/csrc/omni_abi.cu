@@ -74,6 +74,20 @@ int group_heads_for(long long BH, int seqlen, int head_dim) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// cuTensorMapEncodeTiled is a driver call and wants a context current on the calling thread. A
+// thread that has made no runtime call yet (a framework's worker thread that found its buffers in a
+// cache, for instance) has none; setting the runtime's current device again binds the primary context.
+int bind_context() {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaSetDevice(dev);
+  if (e != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(e);
+    return OMNI_ERR_CUDA;
+  }
+  return OMNI_OK;
+}
+
 int forward(bool simple, const void* q, const void* k, const void* v, void* o, float* lse,
             const int32_t* kv_num_blocks, const int32_t* kv_indices, const int32_t* types,
             const int32_t* partial_idx, const uint8_t* partial_bool, const uint32_t* partial_bits, int B,
@@ -106,7 +120,9 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
 
   const bool bf16 = dtype == OMNI_DTYPE_BF16;
   CUtensorMap tmQ, tmK, tmV;
-  int rc = make_tile_map(&tmQ, q, rows, head_dim, bf16);
+  int rc = bind_context();
+  if (rc != OMNI_OK) return rc;
+  rc = make_tile_map(&tmQ, q, rows, head_dim, bf16);
   if (rc != OMNI_OK) return rc;
   rc = make_tile_map(&tmK, k, rows, head_dim, bf16);
   if (rc != OMNI_OK) return rc;
@@ -190,7 +206,9 @@ int backward(const void* q, const void* k, const void* v, const void* o, const f
 
   const bool bf16 = dtype == OMNI_DTYPE_BF16;
   CUtensorMap tmQ, tmK, tmV, tmdO;
-  int rc = make_tile_map(&tmQ, q, rows, head_dim, bf16);
+  int rc = bind_context();
+  if (rc != OMNI_OK) return rc;
+  rc = make_tile_map(&tmQ, q, rows, head_dim, bf16);
   if (rc != OMNI_OK) return rc;
   rc = make_tile_map(&tmK, k, rows, head_dim, bf16);
   if (rc != OMNI_OK) return rc;

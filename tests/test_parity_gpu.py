@@ -426,3 +426,30 @@ def test_flex_block_mask_through_the_kernel(cuda_device):
     dense = mask_mod(0, 0, pos.view(n, 1), pos.view(1, n))
     ref_out, ref_lse = orc.attention_dense_mask(q.float(), k.float(), v.float(), orc.to_score_mask(dense)[None, None])
     assert_parity(out, lse, ref_out, ref_lse, "flex mask")
+
+
+def test_call_from_a_fresh_host_thread(cuda_device):
+    """A host thread that has made no CUDA call of its own (an autograd worker that found its buffers
+    in the allocator's cache, a serving thread) can call the library: the entry points bind the
+    device's primary context themselves before the driver call that builds the TMA descriptors."""
+    import threading
+
+    g = load_golden("ref_causal_n256_d64")
+    q, k, v = (g[n].half().to(cuda_device) for n in ("q", "k", "v"))
+    ref, _ = run(g["q"].half(), g["k"].half(), g["v"].half(), g["bm"], cuda_device)   # also caches the device mask
+    out = torch.empty_like(q)
+    torch.cuda.synchronize()
+    errors = []
+
+    def worker():
+        try:
+            ops.omni_attention_forward_out(q, k, v, out, g["bm"], q.shape[2])
+        except Exception as e:   # noqa: BLE001
+            errors.append(e)
+
+    t = threading.Thread(target=worker)
+    t.start()
+    t.join()
+    torch.cuda.synchronize()
+    assert not errors, errors
+    assert torch.equal(out.cpu(), ref.cpu())
