@@ -221,27 +221,39 @@ def run_ours(args, rank, local_rank, world):
         raise RuntimeError(f"kernel status {int(status.item()):#x}")
 
     # ---- end to end through the public operator with host buffers -------------------------------
+    # Every step copies its q, k, v from pinned host memory, calls the public operator and copies the
+    # output back. Steps alternate between two streams so that one step's device-to-host copy and
+    # kernel run under the next step's host-to-device copy (PCIe is full duplex); every step still
+    # moves all of its own bytes inside the timed region.
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
-    ho = torch.empty_like(hq).pin_memory()
-    e2e_steps = max(3, min(args.steps, 20))
+    e2e_streams = [torch.cuda.Stream(device=dev) for _ in range(2)]
+    ho = [torch.empty_like(hq).pin_memory() for _ in e2e_streams]
+    e2e_steps = max(4, min(args.steps, 20))
 
-    def e2e_step():
-        dq, dk, dv = (t.to(dev, non_blocking=True) for t in (hq, hk, hv))
-        o = omni_attention(dq, dk, dv, bm)
-        ho.copy_(o, non_blocking=True)
+    def e2e_step(i):
+        with torch.cuda.stream(e2e_streams[i & 1]):
+            dq, dk, dv = (t.to(dev, non_blocking=True) for t in (hq, hk, hv))
+            o = omni_attention(dq, dk, dv, bm)
+            ho[i & 1].copy_(o, non_blocking=True)
 
-    for _ in range(3):
-        e2e_step()
+    for i in range(4):
+        e2e_step(i)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    main_stream = torch.cuda.current_stream()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    for st_ in e2e_streams:
+        st_.wait_event(e0)
+    for i in range(e2e_steps):
+        e2e_step(i)
+    for st_ in e2e_streams:
+        main_stream.wait_stream(st_)
     e1.record()
     torch.cuda.synchronize()
     e2e_ms = e0.elapsed_time(e1)
+    assert torch.equal(ho[0], ho[1])   # both streams computed the same inputs
 
     # ---- C5 (32K multi-image), batch*heads sharded over the ranks: strong scaling, reported aside --
     c5 = None
@@ -318,7 +330,8 @@ def run_ours(args, rank, local_rank, world):
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(cfg.name), "peak_source": f"MEASURED_PEAKS.json bf16_tflops ({which}, burst)",
                      "frac_of_nominal_2250": per_gpu_tf / 2250.0},
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": 3 * tensor_bytes, "d2h_bytes_per_step": tensor_bytes,
-                "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
+                "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
+                "streams": 2, "note": "steps alternate between two streams: copies of one step overlap the next step's"},
         "gpu_launches": args.steps,
         "clocks": clocks,
     }
