@@ -50,7 +50,6 @@ constexpr int kBwdComputeThreads = 256;
 constexpr int kBwdThreads = kBwdComputeThreads + 64;
 constexpr int kBwdIssuer = kBwdComputeThreads;         // thread that issues the MMAs
 constexpr int kBwdProducer = kBwdComputeThreads + 32;  // thread that issues the TMA loads
-constexpr bool kBwdDkFirst = false;
 
 // Profiling build (-DOMNI_BWD_PROFILE): the MMA-issuing thread adds up the cycles it spends in each
 // of its waits into 64-bit counters behind the status word (slot + 16 for the dQ kernel).
@@ -398,16 +397,11 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         // E2 of the previous visit has read dP^T (its region takes this visit's S^T) and stored dS^T
         OMNI_BWD_TIMED(0, mbar_wait(bar_ds, ph ^ 1u, abort_flag, p.f.status, 57));
       }
-      if (kBwdDkFirst && i > 0) {
-        tc_fence_after();
-        bwd_mma_ts_split<D>(tdK, tdP, 32, sQ + (stage ^ 1) * Cfg::kTileBytes, idesc_ts, i > 1);      // dK += dS^T(i-1) Q(i-1)
-        tc_commit(bar_dkdone + 8 * (stage ^ 1));
-      }
       OMNI_BWD_TIMED(1, mbar_wait(bar_q + 8 * stage, ld_ph, abort_flag, p.f.status, 51));
       tc_fence_after();
       bwd_mma_ss<D>(tS, sK, sQ + stage * Cfg::kTileBytes, idesc_ss);                                  // S^T(i) = K Q^T
       tc_commit(bar_s);
-      if (!kBwdDkFirst && i > 0) {
+      if (i > 0) {   // after S^T(i), not before: E1(i) is the long pole (dK first measured 7 % slower)
         bwd_mma_ts_split<D>(tdK, tdP, 32, sQ + (stage ^ 1) * Cfg::kTileBytes, idesc_ts, i > 1);      // dK += dS^T(i-1) Q(i-1)
         tc_commit(bar_dkdone + 8 * (stage ^ 1));
       }
