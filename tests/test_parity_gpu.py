@@ -453,3 +453,31 @@ def test_call_from_a_fresh_host_thread(cuda_device):
     torch.cuda.synchronize()
     assert not errors, errors
     assert torch.equal(out.cpu(), ref.cpu())
+
+
+def test_maximum_sequence_length(cuda_device):
+    """1 024 KV blocks = 131 072 tokens, the most the kernels' per-CTA block tables hold: one head, causal
+    lists with a FULL bidirectional band, sampled rows against the scalar oracle; the backward at the same
+    size through the property that needs no oracle."""
+    n, d = 1024 * 128, 64
+    bm = create_causal_omni_block_mask(1, 1, n, n)
+    assert bm.kv_indices.shape == (1, 1, 1024, 1024)
+    gen = torch.Generator().manual_seed(17)
+    q, k, v = (torch.randn(1, 1, n, d, generator=gen).bfloat16() for _ in range(3))
+    out, lse = run(q, k, v, bm, cuda_device)
+    assert out.shape == (1, 1, n, d) and bool(torch.isfinite(out.float()).all())
+    rq = [0, 127, 128, n - 1, n - 128, 65535, 65536, 100000] + torch.randint(0, n, (24,), generator=gen).tolist()
+    rb = [0] * len(rq)
+    so, sl = scalar.oracle_rows(q, k, v, bm, rb, rq)
+    assert_parity(out.float().cpu()[0, 0, rq], lse.cpu()[0, 0, rq], so, sl, "131072 tokens")
+
+    d_out = (torch.randn(1, 1, n, d, generator=gen) * 0.5).bfloat16()
+    qd, kd, vd, dod = (t.to(cuda_device) for t in (q, k, v, d_out))
+    dq, dk, dv = torch.empty_like(qd), torch.empty_like(qd), torch.empty_like(qd)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    ops.omni_attention_backward_out(qd, kd, vd, out.contiguous(), lse.contiguous(), dod, dq, dk, dv, bm, n, None, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert all(bool(torch.isfinite(t.float()).all()) for t in (dq, dk, dv))
+    lhs, rhs = dv.float().sum(dim=2).cpu(), d_out.float().sum(dim=2)
+    assert float((lhs - rhs).abs().max()) <= 2e-2 * float(rhs.abs().max()) + 2.0
