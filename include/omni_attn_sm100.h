@@ -1,4 +1,6 @@
-/* C ABI of the B200 (sm_100a) omni-attention forward library, libomni_attn_sm100.so.
+/* C ABI of the B200 (sm_100a) omni-attention library, libomni_attn_sm100.so: the forward pass (the
+ * reference's operator), and beside it the backward pass and the mask construction, which the
+ * reference does not have as device code.
  *
  * Plain pointers and sizes only; no torch types. Every function returns 0 on success or a negative
  * OMNI_ERR_* code, never throws, allocates no device memory and keeps no reference to its
