@@ -214,13 +214,15 @@ __device__ __forceinline__ int bwd_build_visit_list(const uint32_t* src, long lo
 // scaled raw score is 1 - tanh^2. Replaces the pair of raw scores by their capped raw-equivalents
 // (cap_out * tanh) and returns the two derivative factors.
 __device__ __forceinline__ float2 bwd_soft_cap(float2& s, float cap_in, float cap_out) {
-  const float k = cap_in * 2.8853900817779268f;   // 2 * log2(e)
-  float r0, r1;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(ex2_approx(s.x * k) + 1.f));
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(ex2_approx(s.y * k) + 1.f));
-  const float t0 = fmaf(-2.f, r0, 1.f), t1 = fmaf(-2.f, r1, 1.f);
-  s = make_float2(cap_out * t0, cap_out * t1);
-  return make_float2(fmaf(-t0, t0, 1.f), fmaf(-t1, t1, 1.f));
+  const float2 y = __fmul2_rn(s, make_float2(cap_in, cap_in));
+  float2 t;
+  if (fmaxf(fabsf(y.x), fabsf(y.y)) <= kTanhPolyLimit) {
+    t = tanh_small2(y);   // the forward's polynomial for small arguments: no MUFU work
+  } else {
+    t = make_float2(tanh_exact(y.x), tanh_exact(y.y));
+  }
+  s = __fmul2_rn(t, make_float2(cap_out, cap_out));
+  return __ffma2_rn(make_float2(-t.x, -t.y), t, make_float2(1.f, 1.f));
 }
 
 // CTA index -> (block, batch*head) for the two tile kernels. Heads are taken in groups of

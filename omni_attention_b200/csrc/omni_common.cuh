@@ -214,14 +214,41 @@ __device__ __forceinline__ void apply_allow(const uint32_t (&allow)[4], float (&
 // scale / softcap), so everything downstream is unchanged. tanh(y) = 1 - 2 / (exp(2y) + 1) with
 // ex2.approx and rcp.approx (absolute error around 1e-7; tanh.approx would be 2^-11 relative, too
 // coarse for a log-sum-exp tolerance of 1e-3 once multiplied by the cap).
+// Small arguments, which is what a cap of 50 gives for ordinary scores, do not need the MUFU unit at
+// all: for |y| <= 0.25 the odd Taylor polynomial of degree 7 is within 1e-7 of tanh. Rows whose largest
+// |y| is beyond that take the exact form (a per-thread branch, rare).
+constexpr float kTanhPolyLimit = 0.25f;
+__device__ __forceinline__ float2 tanh_small2(float2 y) {
+  const float2 y2 = __fmul2_rn(y, y);
+  float2 p = __ffma2_rn(y2, make_float2(-17.f / 315.f, -17.f / 315.f), make_float2(2.f / 15.f, 2.f / 15.f));
+  p = __ffma2_rn(p, y2, make_float2(-1.f / 3.f, -1.f / 3.f));
+  p = __ffma2_rn(p, y2, make_float2(1.f, 1.f));
+  return __fmul2_rn(y, p);
+}
+__device__ __forceinline__ float tanh_exact(float y) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(ex2_approx(y * 2.8853900817779268f) + 1.f));   // 2 * log2(e)
+  return fmaf(-2.f, r, 1.f);
+}
+
 __device__ __forceinline__ void soft_cap_scores(float (&s)[128], float cap_in, float cap_out) {
-  const float k = cap_in * 2.8853900817779268f;  // 2 * log2(e)
+  float a = fabsf(s[0]), b = fabsf(s[1]);
 #pragma unroll
-  for (int j = 0; j < 128; ++j) {
-    const float t = ex2_approx(s[j] * k);
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t + 1.f));
-    s[j] = cap_out * fmaf(-2.f, r, 1.f);
+  for (int j = 2; j < 128; j += 2) {
+    a = fmaxf(a, fabsf(s[j]));
+    b = fmaxf(b, fabsf(s[j + 1]));
+  }
+  if (fmaxf(a, b) * cap_in <= kTanhPolyLimit) {
+    const float2 in2 = make_float2(cap_in, cap_in), out2 = make_float2(cap_out, cap_out);
+#pragma unroll
+    for (int j = 0; j < 128; j += 2) {
+      const float2 t = __fmul2_rn(tanh_small2(__fmul2_rn(make_float2(s[j], s[j + 1]), in2)), out2);
+      s[j] = t.x;
+      s[j + 1] = t.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 128; ++j) s[j] = cap_out * tanh_exact(s[j] * cap_in);
   }
 }
 
