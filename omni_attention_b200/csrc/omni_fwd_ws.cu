@@ -248,14 +248,26 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after();
         if (cnt == 0) { OMNI_USTAMP(2); }
 
-        if constexpr (Cfg::kTwoPass && !SOFTCAP) {
-        // pass 1: row maximum over the whole row (the scores are dropped again right away)
+        if constexpr (Cfg::kTwoPass) {
+        // pass 1: row maximum over the whole row (the scores are dropped again right away; with a
+        // soft-cap the capped scores go back to TMEM first, so that pass 2 finds them there)
         float mx;
         {
           float s[128];
           load_scores(tS, s);
+          if constexpr (SOFTCAP) {
+            soft_cap_scores(s, p.cap_in, p.cap_out);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t r[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(s[32 * c + j]);
+              tmem_st32(tS + 32 * c, r);
+            }
+          }
           if (masked) apply_allow(allow, s);
           mx = row_max(s);
+          if constexpr (SOFTCAP) tc_wait_st();
         }
         const float alpha = softmax_update(st, mx, p.scale_log2, kLazyRescaleLog2);
         if (cnt > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) rescale_o<D>(tO, alpha);
@@ -272,7 +284,7 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         st.l = st.l * alpha + sum;
         } else {
-        // one pass with the whole row in registers (with a soft-cap the capped scores are worth keeping)
+        // one pass with the whole row in registers
         float s[128];
         load_scores(tS, s);
         if constexpr (SOFTCAP) soft_cap_scores(s, p.cap_in, p.cap_out);
