@@ -231,18 +231,33 @@ __device__ __forceinline__ float tanh_exact(float y) {
   return fmaf(-2.f, r, 1.f);
 }
 
+__device__ __forceinline__ float absmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(fabsf(b)), "f"(fabsf(c)));
+  return d;
+}
+
 __device__ __forceinline__ void soft_cap_scores(float (&s)[128], float cap_in, float cap_out) {
-  float a = fabsf(s[0]), b = fabsf(s[1]);
+  float a = 0.f, b = 0.f;
 #pragma unroll
-  for (int j = 2; j < 128; j += 2) {
-    a = fmaxf(a, fabsf(s[j]));
-    b = fmaxf(b, fabsf(s[j + 1]));
+  for (int j = 0; j < 128; j += 4) {
+    a = absmax3(a, s[j], s[j + 1]);
+    b = absmax3(b, s[j + 2], s[j + 3]);
   }
   if (fmaxf(a, b) * cap_in <= kTanhPolyLimit) {
-    const float2 in2 = make_float2(cap_in, cap_in), out2 = make_float2(cap_out, cap_out);
+    // cap_out * tanh_small(s * cap_in) with the two factors folded into the coefficients
+    // (cap_in * cap_out = 1): s + s * z * (b1 + z * (b2 + z * b3)), z = s * s
+    const float c2 = cap_in * cap_in;
+    const float b1 = (-1.f / 3.f) * c2, b2 = (2.f / 15.f) * c2 * c2, b3 = (-17.f / 315.f) * c2 * c2 * c2;
+    const float2 b1v = make_float2(b1, b1), b2v = make_float2(b2, b2), b3v = make_float2(b3, b3);
 #pragma unroll
     for (int j = 0; j < 128; j += 2) {
-      const float2 t = __fmul2_rn(tanh_small2(__fmul2_rn(make_float2(s[j], s[j + 1]), in2)), out2);
+      const float2 x = make_float2(s[j], s[j + 1]);
+      const float2 z = __fmul2_rn(x, x);
+      float2 p = __ffma2_rn(z, b3v, b2v);
+      p = __ffma2_rn(p, z, b1v);
+      p = __fmul2_rn(p, z);
+      const float2 t = __ffma2_rn(x, p, x);
       s[j] = t.x;
       s[j + 1] = t.y;
     }
