@@ -297,14 +297,27 @@ def run_ours(args, rank, local_rank, world):
         bwd_ms = time_steps(bstep, 10, 3, flush) / 10
         del d_out, dq, dk, dv, wsp
 
+    # ---- the Transfusion model's variant of the forward (tanh soft-cap 50), reported aside -----------
+    cap_ms = 0.0
+    if not args.no_backward:
+        def cstep():
+            omni_attention_forward_out(q, k, v, out, bm, cfg.N, None, None, status, "ws", softcap=50.0)
+
+        cstep()
+        if world > 1:
+            dist.barrier()
+        cap_ms = time_steps(cstep, 10, 3, flush) / 10
+
     # ---- reduce over ranks (MAX of time, SUM of work) ---------------------------------------------
-    vals = torch.tensor([total_ms, e2e_ms, c5["ms"] if c5 else 0.0, float(flops), bwd_ms], dtype=torch.float64, device=dev)
+    vals = torch.tensor([total_ms, e2e_ms, c5["ms"] if c5 else 0.0, float(flops), bwd_ms, cap_ms], dtype=torch.float64,
+                        device=dev)
     if world > 1:
         mx = vals.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = vals.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         total_ms, e2e_ms, c5ms, flops_all, bwd_ms = float(mx[0]), float(mx[1]), float(mx[2]), float(sm[3]), float(mx[4])
+        cap_ms = float(mx[5])
     else:
         c5ms, flops_all = float(vals[2]), float(flops)
     if rank != 0:
@@ -346,6 +359,9 @@ def run_ours(args, rank, local_rank, world):
                             "launches_per_step": 3, "flop_count": "10*128*128*D per visited block",
                             "roofline_frac": bwd_tf / peak_tf,
                             "kernels": "omni_bwd_prep_kernel, omni_bwd_dkdv_kernel, omni_bwd_dq_kernel"}
+    if cap_ms > 0:
+        line["softcap_forward"] = {"ms": cap_ms, "value": flops_all / (cap_ms * 1e-3) / 1e12, "unit": UNIT, "softcap": 50.0,
+                                   "steps": 10, "roofline_frac": flops / (cap_ms * 1e-3) / 1e12 / peak_tf}
     if world == 1 and not args.no_cpu_baseline:
         torch.set_num_threads(os.cpu_count() or 1)
         line["cpu_baseline"] = cpu_baseline(cfg, bm)
