@@ -242,3 +242,24 @@ def test_backward_through_the_pybind_module(cuda_device):
         assert torch.equal(a.float().cpu(), b)
     with pytest.raises(RuntimeError, match="workspace"):
         m.omni_attn_bwd(q, k, v, out, lse, d_out, dq, dk, dv, nb, idx, typ, 128, 128, N, pidx, pool, True, ws[:16])
+
+
+@pytest.mark.parametrize("n,D", [(128, 64), (128, 128), (200, 128), (640, 64)])
+def test_small_and_odd_shapes_forward_and_backward(cuda_device, n, D):
+    """One Q block, an odd number of Q blocks, a batch*head count that no grouping divides, a length
+    that needs padding: forward and backward against the oracle."""
+    torch.manual_seed(n + D)
+    B, H = 3, 5
+    q, k, v, d_out = (torch.randn(B, H, n, D).half() for _ in range(4))
+    bm = create_causal_omni_block_mask(B, H, n, n)
+    qd, kd, vd = (t.to(cuda_device).requires_grad_(True) for t in (q, k, v))
+    out = omni_attention_autograd(qd, kd, vd, bm)
+    out.backward(d_out.to(cuda_device))
+    n_pad = bm.q_len
+    pad = lambda t: torch.nn.functional.pad(t, (0, 0, 0, n_pad - n))
+    ref_out, _ = orc.block_mask_attention(pad(q), pad(k), pad(v), bm, seqlen_orig=n)
+    err = (out.detach().float().cpu() - ref_out[:, :, :n]).abs()
+    assert float(err.max()) <= 2e-2 + 1e-2 * float(ref_out[:, :, :n].abs().max())
+    ref = orc.block_mask_attention_backward(pad(q), pad(k), pad(v), bm, pad(d_out), seqlen_orig=n)
+    got = tuple(t.grad.float().cpu() for t in (qd, kd, vd))
+    assert_grads(got, tuple(r[:, :, :n] for r in ref), torch.float16, all_heads(B, H), f"n={n} D={D}")
