@@ -481,3 +481,19 @@ def test_maximum_sequence_length(cuda_device):
     assert all(bool(torch.isfinite(t.float()).all()) for t in (dq, dk, dv))
     lhs, rhs = dv.float().sum(dim=2).cpu(), d_out.float().sum(dim=2)
     assert float((lhs - rhs).abs().max()) <= 2e-2 * float(rhs.abs().max()) + 2.0
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("D,dtype", [(128, torch.bfloat16), (64, torch.float16)])
+def test_running_maximum_that_keeps_moving(cuda_device, kernel, D, dtype):
+    """Key magnitude grows with position, so the running maximum of every row rises by far more than the
+    lazy-rescale threshold (2^8) from one KV block to the next: the O rescale path runs on every block."""
+    torch.manual_seed(3)
+    n = 1024
+    q, k, v = (torch.randn(1, 2, n, D) for _ in range(3))
+    k = k * (1.0 + torch.arange(n).float() / 16.0).view(1, 1, n, 1)
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    bm = create_causal_omni_block_mask(1, 2, n, n)
+    out, lse = run(q, k, v, bm, cuda_device, kernel)
+    ref_out, ref_lse = orc.block_mask_attention(q, k, v, bm)
+    assert_parity(out, lse, ref_out, ref_lse, f"moving maximum D={D}")
