@@ -42,12 +42,12 @@ extern "C" {
 #define OMNI_OK 0
 #define OMNI_ERR_NULL_POINTER (-1)     /* a required pointer is NULL */
 #define OMNI_ERR_DTYPE (-2)            /* dtype is neither fp16 nor bf16 */
-#define OMNI_ERR_HEAD_DIM (-3)         /* head_dim not in {64, 128} (32 is accepted by the reference, not built here) */
-#define OMNI_ERR_BLOCK_SIZE (-4)       /* q_block/kv_block differ or are not 128 (64 is accepted by the reference, not built here) */
+#define OMNI_ERR_HEAD_DIM (-3)         /* head_dim not in {32, 64, 128} (omni-attn-mma/mma/omni_attn_shared_kv.cu:725-729); the backward pass takes 64 and 128 */
+#define OMNI_ERR_BLOCK_SIZE (-4)       /* q_block/kv_block differ or are not 64 or 128 (omni_attn_shared_kv.cu:732-741); the backward pass takes 128 */
 #define OMNI_ERR_SEQLEN (-5)           /* seqlen_padded not a positive multiple of the block, or seqlen_orig outside (0, seqlen_padded] */
-#define OMNI_ERR_SHAPE (-6)            /* B, H or max_blocks not positive, or B*H*seqlen too large for 32-bit tile coordinates */
+#define OMNI_ERR_SHAPE (-6)            /* B, H or max_blocks not positive, or B*H > 65535 (backward pass: or B*H*seqlen >= 2^31) */
 #define OMNI_ERR_PARTIAL (-7)          /* num_partial > 0 without any partial mask pool, or num_partial < 0 */
-#define OMNI_ERR_TOO_LONG (-8)         /* more KV blocks per sequence than the kernel's tables hold (1024 blocks = 131072 tokens) */
+#define OMNI_ERR_TOO_LONG (-8)         /* longer than the kernel's block tables hold: see omni_attn_max_seqlen() */
 #define OMNI_ERR_ALIGNMENT (-9)        /* q/k/v/o (or a partial mask pool) not 16-byte aligned */
 #define OMNI_ERR_CUDA (-10)            /* a CUDA runtime/driver call failed; see omni_attn_last_cuda_error() */
 #define OMNI_ERR_NO_DRIVER_ENTRY (-11) /* cuTensorMapEncodeTiled is not available from the driver */
@@ -64,20 +64,26 @@ extern "C" {
 /* Forward pass with the warp-specialised, persistent kernel (work units assigned to the resident
  * CTAs in a fixed pattern; see omni_attn_fwd_scratch_sm100 for dynamic assignment).
  *
- *  q, k, v           [B, H, seqlen_padded, head_dim], contiguous, 16-bit (dtype), device memory
+ *  q, k, v           [B, H, seqlen_padded, head_dim], contiguous, 16-bit (dtype), device memory;
+ *                    head_dim 32, 64 or 128; seqlen_padded a multiple of q_block
  *  o                 same shape and dtype, written in place (rows >= seqlen_orig are zeroed)
  *  lse_or_null       [B, H, seqlen_padded] fp32: natural-log sum of exp of the scaled, masked
  *                    scores of each row (-inf for a row that attends nothing), or NULL.
  *                    The reference has no such output.
- *  kv_num_blocks     [B, H, nq] int32, nq = seqlen_padded / 128
+ *  q_block, kv_block  both 128 or both 64, the two block shapes of the reference's launchers
+ *                    (omni-attn-mma/mma/omni_attn_shared_kv.cu:780-888). The kernels always work on
+ *                    128x128 tiles; lists in 64-blocks are read as they are, a tile being a 2x2 of
+ *                    sub-blocks (no conversion pass, no extra memory).
+ *  kv_num_blocks     [B, H, nq] int32, nq = seqlen_padded / q_block
  *  kv_indices        [B, H, nq, max_blocks] int32; the first kv_num_blocks entries are used
  *  block_mask_types  [B, H, nq, max_blocks] int32 (OMNI_BLOCK_*)
  *  partial_idx_or_null   [B, H, nq, max_blocks] int32 index into the partial pool (-1 = none), or NULL
- *  partial_bool_or_null  [num_partial, 128, 128] one byte per element, non-zero = attend (the
- *                        reference's torch.bool tensor), or NULL
- *  partial_bits_or_null  [num_partial, 128, 4] uint32, bit (c % 32) of word c / 32 of row r = attend;
- *                        produced by omni_attn_pack_partial_masks_sm100. Used in preference to
- *                        the byte form when both are given.
+ *  partial_bool_or_null  [num_partial, q_block, kv_block] one byte per element, non-zero = attend
+ *                        (the reference's torch.bool tensor), or NULL
+ *  partial_bits_or_null  [num_partial, q_block, kv_block / 32] uint32, bit (c % 32) of word c / 32 of
+ *                        row r = attend; produced by omni_attn_pack_partial_masks_sm100 (128-blocks)
+ *                        or omni_attn_pack_partial_masks_blk_sm100. Used in preference to the byte
+ *                        form when both are given.
  *  scale             softmax scale; <= 0 selects 1/sqrt(head_dim), the reference's fixed choice
  *                    (omni-attn-mma/mma/omni_attn_shared_kv.cu:62)
  *  device_status_or_null  one int32 in device memory the kernel may set to an OMNI_STATUS_* value;
@@ -85,7 +91,12 @@ extern "C" {
  *
  * A PARTIAL entry whose index is negative or >= num_partial (or any PARTIAL entry when no pool is
  * given) is treated as CAUSAL, as the reference's dense expansion does
- * (omni-attn-mma/omni_attn_torch.py:140-143). CAUSAL compares absolute positions.
+ * (omni-attn-mma/omni_attn_torch.py:140-143). CAUSAL compares absolute positions. A block that is
+ * listed more than once is visited once, with the meaning the dense expansion gives it when it
+ * applies the entries in list order (:106-143): a later FULL or PARTIAL entry replaces an earlier one, a
+ * diagonal CAUSAL entry counts only for a block that has nothing else (the reference's union of a
+ * PARTIAL mask with a later CAUSAL entry is the one combination not reproduced: the PARTIAL mask stands).
+ * Longest sequence: omni_attn_max_seqlen(head_dim, q_block, 0).
  */
 int omni_attn_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* lse_or_null,
                         const int32_t* kv_num_blocks, const int32_t* kv_indices,
@@ -148,12 +159,14 @@ int omni_attn_fwd_ex_sm100(const void* q, const void* k, const void* v, void* o,
  *  - the array is OMNI_ATTN_SCRATCH_BYTES + OMNI_ATTN_NOALLOC_MAX_PARTIAL * 2048 bytes (about 2 MB) of
  *    device memory on every GPU that loads the library, held until the process exits;
  *  - a byte pool (partial_bool_or_null without partial_bits_or_null) of more than
- *    OMNI_ATTN_NOALLOC_MAX_PARTIAL tiles is refused with OMNI_ERR_NOALLOC_LIMIT before anything is
- *    launched; a pool the caller has already bit-packed may have any size;
+ *    OMNI_ATTN_NOALLOC_MAX_PARTIAL 128x128 tiles (four times as many 64x64 tiles) is refused with
+ *    OMNI_ERR_NOALLOC_LIMIT; a pool the caller has already bit-packed may have any size;
+ *  - every argument check runs before anything is enqueued: a refused call leaves the array alone;
  *  - all calls on a device share the one array and it keeps the previous call's contents: each call
  *    clears the counter and rewrites the packed pool on `cuda_stream` before use. Two calls whose
- *    GPU work can overlap (different streams without an ordering between them, or different host
- *    threads on different streams) race on it and must be serialised by the caller;
+ *    GPU work can overlap (different streams without an ordering between them) race on it and
+ *    must be serialised by the caller. Host threads are serialised by the library itself for the
+ *    time it takes to enqueue one call, so calls from several threads onto ONE stream are safe;
  *  - the first call on each device looks up the array's device address (with that device current);
  *    make that first call before starting any stream capture on the device.
  */
@@ -184,6 +197,26 @@ int omni_attn_fwd_simple_sm100(const void* q, const void* k, const void* v, void
  * ([num_partial,128,4] uint32). Both buffers are device memory owned by the caller. */
 int omni_attn_pack_partial_masks_sm100(const uint8_t* partial_bool, uint32_t* partial_bits,
                                        int num_partial, void* cuda_stream);
+
+/* The same for either block shape of build_partial_block_data: block = 128 or 64
+ * ([num_partial, block, block] bytes -> [num_partial, block, block / 32] uint32). */
+int omni_attn_pack_partial_masks_blk_sm100(const uint8_t* partial_bool, uint32_t* partial_bits,
+                                           int num_partial, int block, void* cuda_stream);
+
+/* Longest seqlen_padded the forward entry points accept for this head_dim (32, 64, 128) and block
+ * shape (64, 128); simple_kernel != 0 asks for omni_attn_fwd_simple_sm100. 0 for unsupported
+ * arguments. The block tables of a sequence live in shared memory beside the tiles, so lists in
+ * 64-blocks, four codes per tile, reach less far (128-blocks: 131072 tokens). The reference's
+ * launchers state no limit (omni-attn-mma/mma/omni_attn_shared_kv.cu:780-1003); its largest
+ * published run is 2048 tokens (omni-attn-mma/logs/printed_mask.md:188-237). */
+int omni_attn_max_seqlen(int head_dim, int block, int simple_kernel);
+
+/* Every wait inside the forward kernels is bounded: a CTA that has waited `cycles` GPU clock cycles
+ * for one hand-over sets *device_status to OMNI_STATUS_WAIT_TIMEOUT | (place << 8), waits for its
+ * own copies and MMAs in flight and exits. The default is 2e9 cycles (about a second); cycles <= 0
+ * restores it. Process-wide, read at every launch. The reference's kernels have no such bound (a
+ * fault there surfaces as a hung or failed launch, omni-attn-mma/mma/omni_attn_shared_kv.cu:1005-1008). */
+void omni_attn_set_wait_cycles(long long cycles);
 
 /* Builds the block mask of an interleaved text / image sequence on the GPU, in the reference's
  * metadata format, from the image span positions. Replaces the host-side builder

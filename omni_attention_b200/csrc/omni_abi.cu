@@ -1,6 +1,7 @@
 // C-ABI layer of libomni_attn_sm100.so: argument validation (the checks of the reference's host
 // launchers, omni-attn-mma/mma/omni_attn_shared_kv.cu:701-753, as error codes instead of
 // exceptions), TMA tensor-map construction and kernel dispatch.
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <cstdlib>
@@ -22,16 +23,14 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 // The driver entry point is looked up at run time so that the library has no link-time
 // dependency on libcuda (it must load on a machine without a driver for symbol checks).
 EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
+  static const EncodeTiledFn fn = [] {   // initialised once, whichever host thread comes first
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult qres;
     cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
-    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    else (void)cudaGetLastError();
-    tried = true;
-  }
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) return reinterpret_cast<EncodeTiledFn>(ptr);
+    (void)cudaGetLastError();
+    return static_cast<EncodeTiledFn>(nullptr);
+  }();
   return fn;
 }
 
@@ -55,22 +54,46 @@ int make_tile_map(CUtensorMap* tm, const void* base, long long rows, int head_di
   return OMNI_OK;
 }
 
+// [BH, N, head_dim] view of one of Q/K/V for the forward kernels; box = 128 rows x 64 columns of one
+// (batch, head), 128-byte swizzle. Rows beyond N and columns beyond head_dim (head_dim 32) read as zeros.
+int make_tile_map_3d(CUtensorMap* tm, const void* base, long long BH, int seqlen, int head_dim, bool bf16) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return OMNI_ERR_NO_DRIVER_ENTRY;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(seqlen),
+                              static_cast<cuuint64_t>(BH)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2,
+                                 static_cast<cuuint64_t>(head_dim) * 2 * static_cast<cuuint64_t>(seqlen)};
+  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return OMNI_ERR_CUDA;
+  }
+  return OMNI_OK;
+}
+
 // Heads per scheduling group of the warp-specialised kernel: as many heads as keep the group's K and
 // V (2 * N * D * 2 bytes per head) inside an L2 budget, 48 MB of the B200's 126 MB unless the
 // environment variable OMNI_ATTN_L2_MB says otherwise.
 int group_heads_for(long long BH, int seqlen, int head_dim) {
-  static long long budget = -1;
-  if (budget < 0) {
+  static const long long budget = [] {
     const char* e = std::getenv("OMNI_ATTN_L2_MB");
     const long long mb = e != nullptr ? std::atoll(e) : 48;
-    budget = (mb > 0 ? mb : 48) << 20;
-  }
+    return (mb > 0 ? mb : 48) << 20;
+  }();
   const long long per_head = 4LL * seqlen * head_dim;
   long long g = budget / per_head;
   if (g < 1) g = 1;
   if (g > BH) g = BH;
   return static_cast<int>(g);
 }
+
+// Cycle budget of the forward kernels' bounded waits (omni_attn_set_wait_cycles).
+std::atomic<long long> g_wait_cycles{kWaitCycleLimit};
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -88,45 +111,64 @@ int bind_context() {
   return OMNI_OK;
 }
 
+// The argument checks of the forward entry points: the list of the reference's launchers
+// (omni-attn-mma/mma/omni_attn_shared_kv.cu:701-753) plus what plain pointers need. Nothing is
+// launched and no CUDA call is made.
+int validate_forward(bool simple, const void* q, const void* k, const void* v, void* o,
+                     const int32_t* kv_num_blocks, const int32_t* kv_indices, const int32_t* types,
+                     const uint8_t* partial_bool, const uint32_t* partial_bits, int B, int H, int seqlen_padded,
+                     int seqlen_orig, int head_dim, int q_block, int kv_block, int max_blocks, int num_partial,
+                     int dtype, const void* scratch, float softcap) {
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || kv_num_blocks == nullptr ||
+      kv_indices == nullptr || types == nullptr) {
+    return OMNI_ERR_NULL_POINTER;
+  }
+  if (dtype != OMNI_DTYPE_F16 && dtype != OMNI_DTYPE_BF16) return OMNI_ERR_DTYPE;
+  if (head_dim != 32 && head_dim != 64 && head_dim != 128) return OMNI_ERR_HEAD_DIM;
+  if (q_block != kv_block || (q_block != 64 && q_block != kBlock)) return OMNI_ERR_BLOCK_SIZE;
+  if (seqlen_padded <= 0 || seqlen_padded % q_block != 0 || seqlen_orig <= 0 || seqlen_orig > seqlen_padded) {
+    return OMNI_ERR_SEQLEN;
+  }
+  if (B <= 0 || H <= 0 || max_blocks <= 0) return OMNI_ERR_SHAPE;
+  const long long BH = static_cast<long long>(B) * H;
+  if (BH > 65535) return OMNI_ERR_SHAPE;
+  if (softcap < 0.f || softcap != softcap) return OMNI_ERR_SOFTCAP;
+  if (simple && softcap > 0.f) return OMNI_ERR_SOFTCAP;
+  if (num_partial < 0) return OMNI_ERR_PARTIAL;
+  if (num_partial > 0 && partial_bool == nullptr && partial_bits == nullptr) return OMNI_ERR_PARTIAL;
+  const bool b64 = q_block == 64;
+  const int nq = (seqlen_padded + kBlock - 1) / kBlock;
+  const int max_tiles = simple ? simple_max_tiles(b64) : ws_max_tiles(head_dim == 128 ? 128 : 64, b64);
+  if (nq > max_tiles) return OMNI_ERR_TOO_LONG;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(partial_bool) ||
+      !aligned16(partial_bits) || !aligned16(scratch)) {
+    return OMNI_ERR_ALIGNMENT;
+  }
+  return OMNI_OK;
+}
+
 int forward(bool simple, const void* q, const void* k, const void* v, void* o, float* lse,
             const int32_t* kv_num_blocks, const int32_t* kv_indices, const int32_t* types,
             const int32_t* partial_idx, const uint8_t* partial_bool, const uint32_t* partial_bits, int B,
             int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block, int kv_block,
             int max_blocks, int num_partial, int dtype, float scale, void* stream, int32_t* status,
             void* scratch, float softcap = 0.f) {
-  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || kv_num_blocks == nullptr ||
-      kv_indices == nullptr || types == nullptr) {
-    return OMNI_ERR_NULL_POINTER;
-  }
-  if (dtype != OMNI_DTYPE_F16 && dtype != OMNI_DTYPE_BF16) return OMNI_ERR_DTYPE;
-  if (head_dim != 64 && head_dim != 128) return OMNI_ERR_HEAD_DIM;
-  if (q_block != kBlock || kv_block != kBlock) return OMNI_ERR_BLOCK_SIZE;
-  if (seqlen_padded <= 0 || seqlen_padded % kBlock != 0 || seqlen_orig <= 0 || seqlen_orig > seqlen_padded) {
-    return OMNI_ERR_SEQLEN;
-  }
-  if (B <= 0 || H <= 0 || max_blocks <= 0) return OMNI_ERR_SHAPE;
+  int rc = validate_forward(simple, q, k, v, o, kv_num_blocks, kv_indices, types, partial_bool, partial_bits, B, H,
+                            seqlen_padded, seqlen_orig, head_dim, q_block, kv_block, max_blocks, num_partial, dtype,
+                            scratch, softcap);
+  if (rc != OMNI_OK) return rc;
   const long long BH = static_cast<long long>(B) * H;
-  const long long rows = BH * seqlen_padded;
-  if (rows >= (1LL << 31) || BH > 65535) return OMNI_ERR_SHAPE;
-  if (simple && softcap > 0.f) return OMNI_ERR_SOFTCAP;
-  if (num_partial < 0) return OMNI_ERR_PARTIAL;
-  if (num_partial > 0 && partial_bool == nullptr && partial_bits == nullptr) return OMNI_ERR_PARTIAL;
-  const int nq = seqlen_padded / kBlock;
-  if (nq > kMaxKvBlocks) return OMNI_ERR_TOO_LONG;
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(partial_bool) ||
-      !aligned16(partial_bits) || !aligned16(scratch)) {
-    return OMNI_ERR_ALIGNMENT;
-  }
-
   const bool bf16 = dtype == OMNI_DTYPE_BF16;
+  // head_dim 32 is computed by the 64-wide kernels: the TMA unit reads the missing columns as zeros
+  const int compute_dim = head_dim == 128 ? 128 : 64;
   CUtensorMap tmQ, tmK, tmV;
-  int rc = bind_context();
+  rc = bind_context();
   if (rc != OMNI_OK) return rc;
-  rc = make_tile_map(&tmQ, q, rows, head_dim, bf16);
+  rc = make_tile_map_3d(&tmQ, q, BH, seqlen_padded, head_dim, bf16);
   if (rc != OMNI_OK) return rc;
-  rc = make_tile_map(&tmK, k, rows, head_dim, bf16);
+  rc = make_tile_map_3d(&tmK, k, BH, seqlen_padded, head_dim, bf16);
   if (rc != OMNI_OK) return rc;
-  rc = make_tile_map(&tmV, v, rows, head_dim, bf16);
+  rc = make_tile_map_3d(&tmV, v, BH, seqlen_padded, head_dim, bf16);
   if (rc != OMNI_OK) return rc;
 
   FwdParams p;
@@ -145,7 +187,7 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
   p.BH = static_cast<int>(BH);
   p.N = seqlen_padded;
   p.seqlen_orig = seqlen_orig;
-  p.nq = nq;
+  p.nq = (seqlen_padded + kBlock - 1) / kBlock;
   p.max_blocks = max_blocks;
   p.num_partial = num_partial;
   p.scale = scale > 0.f ? scale : 1.f / std::sqrt(static_cast<float>(head_dim));
@@ -154,10 +196,14 @@ int forward(bool simple, const void* q, const void* k, const void* v, void* o, f
   p.cap_in = softcap > 0.f ? p.scale / softcap : 0.f;
   p.cap_out = softcap > 0.f ? softcap / p.scale : 0.f;
   p.group_heads = group_heads_for(BH, seqlen_padded, head_dim);
+  p.d_real = head_dim;
+  p.blk64 = q_block == 64 ? 1 : 0;
+  p.nq_lists = seqlen_padded / q_block;
+  p.wait_cycles = g_wait_cycles.load(std::memory_order_relaxed);
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = simple ? launch_simple(head_dim, bf16, tmQ, tmK, tmV, p, st)
-                         : launch_ws(head_dim, bf16, tmQ, tmK, tmV, p, st);
+  cudaError_t e = simple ? launch_simple(compute_dim, bf16, tmQ, tmK, tmV, p, st)
+                         : launch_ws(compute_dim, bf16, tmQ, tmK, tmV, p, st);
   if (e != cudaSuccess) {
     g_last_cuda_error = static_cast<int>(e);
     return OMNI_ERR_CUDA;
@@ -243,6 +289,10 @@ int backward(const void* q, const void* k, const void* v, const void* o, const f
   p.f.group_heads = group_heads_for(BH, seqlen_padded, head_dim) / 2 > 0 ? group_heads_for(BH, seqlen_padded, head_dim) / 2 : 1;
   p.f.num_units = 0;
   p.f.o_aligned32 = 0;
+  p.f.d_real = head_dim;
+  p.f.blk64 = 0;
+  p.f.nq_lists = nq;
+  p.f.wait_cycles = kWaitCycleLimit;
   p.o = o;
   p.d_o = d_o;
   p.lse = lse;
@@ -338,13 +388,14 @@ int omni_attn_fwd_simple_sm100(const void* q, const void* k, const void* v, void
                        dtype, scale, cuda_stream, device_status_or_null, nullptr);
 }
 
-int omni_attn_pack_partial_masks_sm100(const uint8_t* partial_bool, uint32_t* partial_bits,
-                                       int num_partial, void* cuda_stream) {
+int omni_attn_pack_partial_masks_blk_sm100(const uint8_t* partial_bool, uint32_t* partial_bits,
+                                           int num_partial, int block, void* cuda_stream) {
+  if (block != 64 && block != omni::kBlock) return OMNI_ERR_BLOCK_SIZE;
   if (num_partial < 0) return OMNI_ERR_PARTIAL;
   if (num_partial == 0) return OMNI_OK;
   if (partial_bool == nullptr || partial_bits == nullptr) return OMNI_ERR_NULL_POINTER;
   if (!omni::aligned16(partial_bool) || !omni::aligned16(partial_bits)) return OMNI_ERR_ALIGNMENT;
-  const long long n_words = static_cast<long long>(num_partial) * omni::kBlock * 4;
+  const long long n_words = static_cast<long long>(num_partial) * block * (block / 32);
   const int threads = 256;
   const long long blocks = (n_words + threads - 1) / threads;
   omni::pack_partial_kernel<<<static_cast<unsigned>(blocks), threads, 0,
@@ -355,6 +406,11 @@ int omni_attn_pack_partial_masks_sm100(const uint8_t* partial_bool, uint32_t* pa
     return OMNI_ERR_CUDA;
   }
   return OMNI_OK;
+}
+
+int omni_attn_pack_partial_masks_sm100(const uint8_t* partial_bool, uint32_t* partial_bits,
+                                       int num_partial, void* cuda_stream) {
+  return omni_attn_pack_partial_masks_blk_sm100(partial_bool, partial_bits, num_partial, omni::kBlock, cuda_stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -411,15 +467,30 @@ int omni_attn_fwd_noalloc_sm100(const void* q, const void* k, const void* v, voi
                                 int B, int H, int seqlen_padded, int seqlen_orig, int head_dim, int q_block,
                                 int kv_block, int max_blocks, int num_partial, int dtype, float scale,
                                 void* cuda_stream, int32_t* device_status_or_null) {
-  const bool pack_here = num_partial > 0 && partial_bits_or_null == nullptr && partial_bool_or_null != nullptr;
-  if (pack_here && num_partial > OMNI_ATTN_NOALLOC_MAX_PARTIAL) return OMNI_ERR_NOALLOC_LIMIT;
-  unsigned char* scratch = nullptr;
-  int rc = omni::builtin_scratch_address(&scratch);
+  // Every argument check comes first: a call that is going to be refused must not have touched the
+  // shared array.
+  int rc = omni::validate_forward(false, q, k, v, o, kv_num_blocks, kv_indices, block_mask_types, partial_bool_or_null,
+                                  partial_bits_or_null, B, H, seqlen_padded, seqlen_orig, head_dim, q_block, kv_block,
+                                  max_blocks, num_partial, dtype, nullptr, 0.f);
   if (rc != OMNI_OK) return rc;
+  const bool pack_here = num_partial > 0 && partial_bits_or_null == nullptr && partial_bool_or_null != nullptr;
+  // room for OMNI_ATTN_NOALLOC_MAX_PARTIAL bit-packed 128x128 tiles; a 64x64 tile takes a quarter of one
+  const long long tile_bytes = static_cast<long long>(q_block) * q_block / 8;
+  if (pack_here && num_partial * tile_bytes > static_cast<long long>(OMNI_ATTN_NOALLOC_MAX_PARTIAL) * omni::kBlock * 16) {
+    return OMNI_ERR_NOALLOC_LIMIT;
+  }
+  unsigned char* scratch = nullptr;
+  rc = omni::builtin_scratch_address(&scratch);
+  if (rc != OMNI_OK) return rc;
+  // The pack and the forward are two enqueues that belong together: without the lock two host
+  // threads on one stream could interleave them (pack A, pack B, forward A, forward B) and A would
+  // read B's masks although nothing overlaps on the GPU.
+  static std::mutex enqueue_mu;
+  std::lock_guard<std::mutex> lock(enqueue_mu);
   const uint32_t* bits = partial_bits_or_null;
   if (pack_here) {
     uint32_t* pool = reinterpret_cast<uint32_t*>(scratch + omni::kBuiltinPoolOffset);
-    rc = omni_attn_pack_partial_masks_sm100(partial_bool_or_null, pool, num_partial, cuda_stream);
+    rc = omni_attn_pack_partial_masks_blk_sm100(partial_bool_or_null, pool, num_partial, q_block, cuda_stream);
     if (rc != OMNI_OK) return rc;
     bits = pool;
   }
@@ -427,6 +498,17 @@ int omni_attn_fwd_noalloc_sm100(const void* q, const void* k, const void* v, voi
                        partial_idx_or_null, partial_bool_or_null, bits, B, H, seqlen_padded, seqlen_orig,
                        head_dim, q_block, kv_block, max_blocks, num_partial, dtype, scale, cuda_stream,
                        device_status_or_null, scratch);
+}
+
+void omni_attn_set_wait_cycles(long long cycles) {
+  omni::g_wait_cycles.store(cycles > 0 ? cycles : omni::kWaitCycleLimit, std::memory_order_relaxed);
+}
+
+int omni_attn_max_seqlen(int head_dim, int block, int simple_kernel) {
+  if ((head_dim != 32 && head_dim != 64 && head_dim != 128) || (block != 64 && block != omni::kBlock)) return 0;
+  const bool b64 = block == 64;
+  const int tiles = simple_kernel ? omni::simple_max_tiles(b64) : omni::ws_max_tiles(head_dim == 128 ? 128 : 64, b64);
+  return tiles * omni::kBlock;
 }
 
 long long omni_attn_bwd_workspace_bytes(int B, int H, int seqlen_padded) {
@@ -467,12 +549,17 @@ const char* omni_attn_error_string(int code) {
     case OMNI_OK: return "ok";
     case OMNI_ERR_NULL_POINTER: return "a required pointer is NULL";
     case OMNI_ERR_DTYPE: return "dtype must be fp16 (0) or bf16 (1)";
-    case OMNI_ERR_HEAD_DIM: return "head_dim must be 64 or 128";
-    case OMNI_ERR_BLOCK_SIZE: return "Q_BLOCK_SIZE and KV_BLOCK_SIZE must both be 128";
-    case OMNI_ERR_SEQLEN: return "seqlen_padded must be a positive multiple of 128 and 0 < seqlen_orig <= seqlen_padded";
-    case OMNI_ERR_SHAPE: return "B, H, max_blocks must be positive, B*H <= 65535 and B*H*seqlen < 2^31";
+    case OMNI_ERR_HEAD_DIM: return "head_dim must be 32, 64 or 128 (backward pass: 64 or 128)";
+    case OMNI_ERR_BLOCK_SIZE:
+      return "Q_BLOCK_SIZE and KV_BLOCK_SIZE must be equal and 64 or 128 (backward pass and pack: see the header)";
+    case OMNI_ERR_SEQLEN:
+      return "seqlen_padded must be a positive multiple of the block size and 0 < seqlen_orig <= seqlen_padded";
+    case OMNI_ERR_SHAPE:
+      return "B, H, max_blocks must be positive and B*H <= 65535 (backward pass: also B*H*seqlen < 2^31)";
     case OMNI_ERR_PARTIAL: return "num_partial is negative, or positive without a partial mask pool";
-    case OMNI_ERR_TOO_LONG: return "sequence longer than 1024 KV blocks (131072 tokens)";
+    case OMNI_ERR_TOO_LONG:
+      return "sequence longer than the kernel's block tables hold (131072 tokens with 128-blocks; see "
+             "omni_attn_max_seqlen)";
     case OMNI_ERR_ALIGNMENT: return "q, k, v, o and the partial mask pools must be 16-byte aligned";
     case OMNI_ERR_CUDA: return "a CUDA call failed (see omni_attn_last_cuda_error)";
     case OMNI_ERR_NO_DRIVER_ENTRY: return "cuTensorMapEncodeTiled not available from the CUDA driver";

@@ -4,8 +4,9 @@
 // unchanged. Each one validates its tensors the way the reference launchers do
 // (omni-attn-mma/mma/omni_attn_shared_kv.cu:701-753, omni-attn-mma/mma/attn_naive.cu:312-356;
 // failures raise std::runtime_error -> RuntimeError) and forwards to the C ABI of
-// libomni_attn_sm100.so. Differences from the reference, all supersets: bf16 is accepted as well
-// as fp16, the launch goes to torch's current stream instead of the legacy default stream, and
+// libomni_attn_sm100.so. Both block shapes (64x64, 128x128) and all three head dimensions (32, 64, 128)
+// of the reference's launchers are taken as they are. Differences from the reference, all supersets:
+// bf16 is accepted as well as fp16, the launch goes to torch's current stream instead of the legacy default stream, and
 // `omni_attn_fwd` adds optional scale / log-sum-exp / status arguments; `omni_attn_bwd` is the backward pass.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -69,7 +70,6 @@ void forward_impl(bool simple, const torch::Tensor& Q, const torch::Tensor& K, c
   if (Q_BLOCK_SIZE != KV_BLOCK_SIZE || (Q_BLOCK_SIZE != 64 && Q_BLOCK_SIZE != 128)) {
     fail("Unsupported block size combination: Q_BLOCK_SIZE and KV_BLOCK_SIZE must be equal and 64 or 128");
   }
-  if (Q_BLOCK_SIZE == 64) fail("64x64 blocks are accepted by the reference but not built for sm_100a; use 128");
   const int nq = (N + Q_BLOCK_SIZE - 1) / Q_BLOCK_SIZE;
   if (kv_num_blocks.dim() != 3 || kv_num_blocks.size(0) != B || kv_num_blocks.size(1) != H ||
       kv_num_blocks.size(2) != nq) {
@@ -81,7 +81,6 @@ void forward_impl(bool simple, const torch::Tensor& Q, const torch::Tensor& K, c
   }
   if (N % Q_BLOCK_SIZE != 0) fail("sequence length must be padded to a multiple of the block size");
   if (D != 32 && D != 64 && D != 128) fail("Unsupported head_dim: must be 32, 64 or 128");
-  if (D == 32) fail("head_dim 32 is accepted by the reference but not built for sm_100a; use 64 or 128");
   if (kv_indices.dim() != 4 || kv_indices.size(0) != B || kv_indices.size(1) != H || kv_indices.size(2) != nq) {
     fail("kv_indices must be [B, H, num_q_blocks, max_blocks]");
   }
@@ -112,8 +111,8 @@ void forward_impl(bool simple, const torch::Tensor& Q, const torch::Tensor& K, c
     if (partial_bits.has_value() && num_partial > 0) {
       const auto& pb = *partial_bits;
       if (!pb.is_cuda() || !pb.is_contiguous() || pb.scalar_type() != torch::kInt32 ||
-          pb.numel() != static_cast<int64_t>(num_partial) * 128 * 4) {
-        fail("partial_bits must be a contiguous CUDA int32 tensor [num_partial, 128, 4]");
+          pb.numel() != static_cast<int64_t>(num_partial) * Q_BLOCK_SIZE * (KV_BLOCK_SIZE / 32)) {
+        fail("partial_bits must be a contiguous CUDA int32 tensor [num_partial, Q_BLOCK_SIZE, KV_BLOCK_SIZE / 32]");
       }
       pbits = reinterpret_cast<const uint32_t*>(pb.data_ptr<int32_t>());
     }
@@ -166,6 +165,10 @@ void forward_impl(bool simple, const torch::Tensor& Q, const torch::Tensor& K, c
 OMNI_DEFINE_REFERENCE_ENTRY(omni_attn_mma_stages_split_q_shared_kv, false)
 OMNI_DEFINE_REFERENCE_ENTRY(omni_attn_mma_stages_split_q_shared_kv_swizzle, false)
 OMNI_DEFINE_REFERENCE_ENTRY(omni_attn_preftech_kernel, false)
+// The reference's wrapper omni_attention_preftech imports this name (omni-attn-mma/omni_attn_torch.py:978),
+// which the reference's own binding does not export (it only works there through the wrapper's
+// load-the-.so-by-path fallback, :999); exporting it lets the unmodified wrapper run.
+OMNI_DEFINE_REFERENCE_ENTRY(omni_attn_preftech, false)
 OMNI_DEFINE_REFERENCE_ENTRY(omni_attn_cp_async, false)
 OMNI_DEFINE_REFERENCE_ENTRY(omni_attn_simple_kernel, true)
 
@@ -275,6 +278,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("omni_attn_simple_kernel", &omni_attn_simple_kernel, "omni_attn_simple_kernel");
   m.def("omni_attn_cp_async", &omni_attn_cp_async, "omni_attn_cp_async");
   m.def("omni_attn_preftech_kernel", &omni_attn_preftech_kernel, "omni_attn_preftech_kernel");
+  m.def("omni_attn_preftech", &omni_attn_preftech, "omni_attn_preftech");
   m.def("omni_attn_mma_stages_split_q_shared_kv_swizzle", &omni_attn_mma_stages_split_q_shared_kv_swizzle,
         "omni_attn_mma_stages_split_q_shared_kv_swizzle");
   m.def("omni_attn_fwd", &omni_attn_fwd, "forward with optional scale / lse / status / bit-packed partial masks",

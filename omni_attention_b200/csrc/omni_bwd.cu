@@ -51,18 +51,6 @@ constexpr int kBwdThreads = kBwdComputeThreads + 64;
 constexpr int kBwdIssuer = kBwdComputeThreads;         // thread that issues the MMAs
 constexpr int kBwdProducer = kBwdComputeThreads + 32;  // thread that issues the TMA loads
 
-// Profiling build (-DOMNI_BWD_PROFILE): the MMA-issuing thread adds up the cycles it spends in each
-// of its waits into 64-bit counters behind the status word (slot + 16 for the dQ kernel).
-#ifdef OMNI_BWD_PROFILE
-#define OMNI_BWD_TIMED(slot, call)                                                              \
-  do {                                                                                          \
-    const long long t_begin_ = clock64();                                                       \
-    call;                                                                                       \
-    prof_acc[slot] += clock64() - t_begin_;                                                     \
-  } while (0)
-#else
-#define OMNI_BWD_TIMED(slot, call) call
-#endif
 
 template <bool BF16>
 __device__ __forceinline__ float2 unpack2(uint32_t w) {
@@ -89,10 +77,14 @@ __global__ void __launch_bounds__(128) omni_bwd_prep_kernel(const BwdParams p) {
   const long long list_base = (static_cast<long long>(bh) * nq + qb) * p.f.max_blocks;
   int n_list = __ldg(p.f.kv_num_blocks + static_cast<long long>(bh) * nq + qb);
   n_list = max(0, min(n_list, p.f.max_blocks));
-  for (int i = tid; i < n_list; i += 128) {
-    int kvb;
-    const uint32_t code = resolve_entry(p.f, list_base, i, qb, kvb);
-    if (code != 0u) codes[kvb] = code;
+  if (tid < 32) {   // one warp walks the list in order; a block listed twice resolves as in the forward
+    for (int i0 = 0; i0 < n_list; i0 += 32) {
+      const int i = i0 + tid;
+      int kvb = -1;
+      uint32_t code = 0u;
+      if (i < n_list) code = resolve_entry(p.f, list_base, i, qb, kvb);
+      table_put(codes, code != 0u ? kvb : -1, code);
+    }
   }
 
   // delta: one warp per row at a time, D / 32 elements per lane
@@ -383,10 +375,6 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
   } else if (tid == kBwdIssuer) {
     // =========================== MMA issuer ======================================================
-#ifdef OMNI_BWD_PROFILE
-    long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long prof_t0 = clock64();
-#endif
     for (int i = 0; i < n_vis; ++i) {
       const int stage = i & 1;
       const uint32_t ph = static_cast<uint32_t>(i & 1);
@@ -397,9 +385,9 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         mbar_wait(bar_kv, 0, abort_flag, p.f.status, 50);
       } else {
         // E2 of the previous visit has read dP^T (its region takes this visit's S^T) and stored dS^T
-        OMNI_BWD_TIMED(0, mbar_wait(bar_ds, ph ^ 1u, abort_flag, p.f.status, 57));
+        mbar_wait(bar_ds, ph ^ 1u, abort_flag, p.f.status, 57);
       }
-      OMNI_BWD_TIMED(1, mbar_wait(bar_q + 8 * stage, ld_ph, abort_flag, p.f.status, 51));
+      mbar_wait(bar_q + 8 * stage, ld_ph, abort_flag, p.f.status, 51);
       tc_fence_after();
       bwd_mma_ss<D>(tS, sK, sQ + stage * Cfg::kTileBytes, idesc_ss);                                  // S^T(i) = K Q^T
       tc_commit(bar_s);
@@ -407,11 +395,11 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         bwd_mma_ts_split<D>(tdK, tdP, 32, sQ + (stage ^ 1) * Cfg::kTileBytes, idesc_ts, i > 1);      // dK += dS^T(i-1) Q(i-1)
         tc_commit(bar_dkdone + 8 * (stage ^ 1));
       }
-      OMNI_BWD_TIMED(2, mbar_wait(bar_do + 8 * stage, ld_ph, abort_flag, p.f.status, 52));
+      mbar_wait(bar_do + 8 * stage, ld_ph, abort_flag, p.f.status, 52);
       tc_fence_after();
       bwd_mma_ss<D>(tdP, sV, sdO + stage * Cfg::kTileBytes, idesc_ss);                                // dP^T(i) = V dO^T
       tc_commit(bar_dp);
-      OMNI_BWD_TIMED(3, mbar_wait(bar_p, ph, abort_flag, p.f.status, 58));
+      mbar_wait(bar_p, ph, abort_flag, p.f.status, 58);
       tc_fence_after();
       bwd_mma_ts_split<D>(tdV, tS, 0, sdO + stage * Cfg::kTileBytes, idesc_ts, i > 0);               // dV += P^T(i) dO(i)
       tc_commit(bar_dvdone + 8 * stage);
@@ -425,28 +413,12 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // keep this thread alive until every MMA has retired
       mbar_wait(bar_dkdone + 8 * (last & 1), static_cast<uint32_t>((last >> 1) & 1), abort_flag, p.f.status, 59);
     }
-#ifdef OMNI_BWD_PROFILE
-    if (p.f.status != nullptr) {
-      unsigned long long* prof = reinterpret_cast<unsigned long long*>(p.f.status + 4);
-      for (int j = 0; j < 4; ++j) atomicAdd(prof + j, static_cast<unsigned long long>(prof_acc[j]));
-      atomicAdd(prof + 4, static_cast<unsigned long long>(clock64() - prof_t0));
-      atomicAdd(prof + 5, static_cast<unsigned long long>(n_vis));
-    }
-#endif
   } else if (compute) {
     // =========================== per-element work ================================================
     const int k_abs = kvb * kBlock + t;
     const bool key_live = k_abs < p.f.seqlen_orig;
     const float2 c2 = make_float2(p.f.scale_log2, p.f.scale_log2);
-#ifdef OMNI_BWD_PROFILE
-    long long cprof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long ct = clock64();
-#define OMNI_CSTAMP(j) if (tid == 0) { const long long now_ = clock64(); cprof[j] += now_ - ct; ct = now_; }
-#else
-#define OMNI_CSTAMP(j)
-#endif
     for (int i = 0; i < n_vis; ++i) {
-      OMNI_CSTAMP(0);
       const int stage = i & 1;
       const uint32_t ph = static_cast<uint32_t>(i & 1);
       const int qb = vis_s[i];
@@ -507,10 +479,8 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const float* lse_c = lse_s + stage * kBlock + 64 * half;
       const float* del_c = delta_s + stage * kBlock + 64 * half;
       float pf[64];      // the unrounded probabilities (times the soft-cap slope, if any), kept for E2
-      OMNI_CSTAMP(1);
       mbar_wait_warp(bar_s, ph, abort_flag, p.f.status, 52);
       tc_fence_after();
-      OMNI_CSTAMP(2);
       auto e1 = [&](auto masked_c) {
         constexpr bool kMasked = decltype(masked_c)::value;
         uint32_t rs2[2][32];
@@ -552,12 +522,10 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p);
-      OMNI_CSTAMP(3);
 
       // ---- E2: dS^T ------------------------------------------------------------------------------
       mbar_wait_warp(bar_dp, ph, abort_flag, p.f.status, 53);
       tc_fence_after();
-      OMNI_CSTAMP(4);
       uint32_t rd2[2][32];
       tmem_ld32(my_dp, rd2[0]);
       tmem_ld32(my_dp + 32, rd2[1]);
@@ -580,7 +548,6 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_ds);
-      OMNI_CSTAMP(5);
 
       // the vectors (and the partial-mask bits) of this visit are free once every compute thread is
       // through E2
@@ -589,14 +556,7 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         lse_s[stage * kBlock + tid] = next_lse == -INFINITY ? INFINITY : next_lse;
         delta_s[stage * kBlock + tid] = next_delta;
       }
-      OMNI_CSTAMP(6);
     }
-#ifdef OMNI_BWD_PROFILE
-    if (tid == 0 && p.f.status != nullptr) {
-      unsigned long long* prof = reinterpret_cast<unsigned long long*>(p.f.status + 4) + 32;
-      for (int j = 0; j < 7; ++j) atomicAdd(prof + j, static_cast<unsigned long long>(cprof[j]));
-    }
-#endif
     if (n_vis > 0) {
       const int last = n_vis - 1;
       mbar_wait_warp(bar_dkdone + 8 * (last & 1), static_cast<uint32_t>((last >> 1) & 1), abort_flag, p.f.status, 54);
@@ -749,18 +709,14 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else if (tid == kBwdIssuer) {
     // =========================== MMA issuer ======================================================
-#ifdef OMNI_BWD_PROFILE
-    long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long prof_t0 = clock64();
-#endif
     auto issue_s = [&](int j) {    // S(j) = Q K(j)^T
-      OMNI_BWD_TIMED(1, mbar_wait(bar_k + 8 * (j % 3), static_cast<uint32_t>((j / 3) & 1), abort_flag, p.f.status, 61));
+      mbar_wait(bar_k + 8 * (j % 3), static_cast<uint32_t>((j / 3) & 1), abort_flag, p.f.status, 61);
       tc_fence_after();
       bwd_mma_ss<D>(region_s(j), sQ, sK + (j % 3) * Cfg::kTileBytes, idesc_ss);
       tc_commit(bar_s + 8 * (j & 1));
     };
     auto issue_dp = [&](int j) {   // dP(j) = dO V(j)^T
-      OMNI_BWD_TIMED(2, mbar_wait(bar_v + 8 * (j & 1), static_cast<uint32_t>((j >> 1) & 1), abort_flag, p.f.status, 62));
+      mbar_wait(bar_v + 8 * (j & 1), static_cast<uint32_t>((j >> 1) & 1), abort_flag, p.f.status, 62);
       tc_fence_after();
       bwd_mma_ss<D>(region_dp(j), sdO, sV + (j & 1) * Cfg::kTileBytes, idesc_ss);
       tc_commit(bar_dp);
@@ -773,7 +729,7 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (n_vis > 1) issue_s(1);
     }
     for (int i = 0; i < n_vis; ++i) {
-      OMNI_BWD_TIMED(0, mbar_wait(bar_ds, static_cast<uint32_t>(i & 1), abort_flag, p.f.status, 63));
+      mbar_wait(bar_ds, static_cast<uint32_t>(i & 1), abort_flag, p.f.status, 63);
       tc_fence_after();
       if (i + 1 < n_vis) issue_dp(i + 1);   // first: E2(i+1) is waiting for it
       bwd_mma_ts_split<D>(tdQ, region_s(i), 0, sK + (i % 3) * Cfg::kTileBytes, idesc_ts, i > 0);   // dQ += dS(i) K(i)
@@ -784,14 +740,6 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int last = n_vis - 1;
       mbar_wait(bar_kfree + 8 * (last % 3), static_cast<uint32_t>((last / 3) & 1), abort_flag, p.f.status, 64);
     }
-#ifdef OMNI_BWD_PROFILE
-    if (p.f.status != nullptr) {
-      unsigned long long* prof = reinterpret_cast<unsigned long long*>(p.f.status + 4) + 16;
-      for (int j = 0; j < 4; ++j) atomicAdd(prof + j, static_cast<unsigned long long>(prof_acc[j]));
-      atomicAdd(prof + 4, static_cast<unsigned long long>(clock64() - prof_t0));
-      atomicAdd(prof + 5, static_cast<unsigned long long>(n_vis));
-    }
-#endif
   } else if (compute) {
     // =========================== per-element work ================================================
     const int q_abs = qb * kBlock + t;
@@ -896,8 +844,8 @@ static cudaError_t launch_bwd_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, 
   using Cfg = BwdCfg<D>;
   auto dkdv = omni_bwd_dkdv_kernel<D, BF16, SOFTCAP>;
   auto dq = omni_bwd_dq_kernel<D, BF16, SOFTCAP>;
-  static bool attr_dkdv[64] = {};
-  static bool attr_dq[64] = {};
+  static SmemAttrOnce attr_dkdv[kMaxDevices];
+  static SmemAttrOnce attr_dq[kMaxDevices];
   cudaError_t e = ensure_smem_attr(dkdv, Cfg::kSmemBytes, attr_dkdv);
   if (e != cudaSuccess) return e;
   e = ensure_smem_attr(dq, DqCfg<D>::kSmemBytes, attr_dq);

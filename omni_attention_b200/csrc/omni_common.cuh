@@ -42,9 +42,9 @@ struct FwdParams {
   int32_t* status;                // device status word or null
   int32_t* unit_counter;          // zeroed int32 in caller scratch for dynamic unit hand-out, or null
   int BH;
-  int N;            // padded sequence length (multiple of 128)
+  int N;            // padded sequence length (multiple of 128; of 64 with blk64)
   int seqlen_orig;  // unpadded length
-  int nq;           // N / 128
+  int nq;           // ceil(N / 128): 128-row tiles per (batch, head)
   int max_blocks;
   int num_partial;
   float scale;           // softmax scale
@@ -55,6 +55,11 @@ struct FwdParams {
   int group_heads;       // heads per scheduling group of the warp-specialised kernel (>= 1)
   int num_units;         // work units of the warp-specialised kernel: ceil(nq / 2) * BH
   int o_aligned32;       // output base address is 32-byte aligned (256-bit stores allowed)
+  int d_real;            // head_dim of the tensors in memory: 32, 64 or 128 (32 is computed as 64 with the
+                         // missing columns read as zeros by the TMA unit); row pitch of o is d_real * 2 bytes
+  int blk64;             // 1: the lists, types and partial pool are in 64x64 blocks (N a multiple of 64)
+  int nq_lists;          // Q blocks in the lists: N / 64 with blk64, else nq
+  long long wait_cycles; // cycle budget of one bounded wait in the forward kernels
 };
 
 // Launch parameters of the backward kernels. `f` carries the block lists, the partial-mask pools,
@@ -72,18 +77,21 @@ struct BwdParams {
   float* delta;        // workspace: [BH, N] rowsum(dO * O)
 };
 
-// Resolve entry `i` of the list of (bh, qb). Returns 0 when the entry is not visited.
-__device__ __forceinline__ uint32_t resolve_entry(const FwdParams& p, long long list_base, int i,
-                                                  int qb, int& kvb_out) {
+// Resolve entry `i` of the list of (bh, qb) for lists in BLK x BLK blocks. Returns 0 when the entry is
+// not visited.
+template <int BLK>
+__device__ __forceinline__ uint32_t resolve_entry_blk(const FwdParams& p, long long list_base, int i,
+                                                      int qb, int& kvb_out) {
   const int kvb = __ldg(p.kv_indices + list_base + i);
   int t = __ldg(p.types + list_base + i);
   kvb_out = kvb;
-  if (kvb < 0 || kvb >= p.nq) {
+  const int n_kv_blocks = BLK == kBlock ? p.nq : p.nq_lists;
+  if (kvb < 0 || kvb >= n_kv_blocks) {
     if (p.status != nullptr) atomicCAS(p.status, 0, kStatusBadIndex);
     return 0;
   }
   if (t <= kTypeMasked || t > kTypePartial) return 0;
-  const int kv_start = kvb * kBlock;
+  const int kv_start = kvb * BLK;
   if (kv_start >= p.seqlen_orig) return 0;
   uint32_t pidx = 0;
   if (t == kTypePartial) {
@@ -104,8 +112,75 @@ __device__ __forceinline__ uint32_t resolve_entry(const FwdParams& p, long long 
       return 0;
     }
   }
-  const uint32_t clip = (kv_start + kBlock > p.seqlen_orig) ? kCodeClip : 0u;
+  const uint32_t clip = (kv_start + BLK > p.seqlen_orig) ? kCodeClip : 0u;
   return static_cast<uint32_t>(t) | clip | (pidx << 3);
+}
+
+__device__ __forceinline__ uint32_t resolve_entry(const FwdParams& p, long long list_base, int i,
+                                                  int qb, int& kvb_out) {
+  return resolve_entry_blk<kBlock>(p, list_base, i, qb, kvb_out);
+}
+
+// Warp-collective write of one resolved entry per lane into a code table (`idx` < 0: this lane has
+// nothing to write). A block that is listed more than once gets the meaning the reference's dense
+// expansion gives it when it applies the entries in list order (omni-attn-mma/omni_attn_torch.py:
+// 106-143): a FULL entry, a CAUSAL entry below the diagonal and a PARTIAL entry with its element mask
+// replace whatever the block had (`strong`), a diagonal CAUSAL entry only adds to it, so it counts
+// only for a block that has nothing yet. (The one combination this does not reproduce is a diagonal
+// CAUSAL entry listed after a PARTIAL one for the same block: the reference takes the union, here the
+// PARTIAL mask stands.) Callers feed the list 32 entries at a time, in order.
+__device__ __forceinline__ void table_put(uint32_t* tab, int idx, uint32_t code) {
+  const int lane = threadIdx.x & 31;
+  const bool strong = idx >= 0 && (code & kCodeTypeMask) != kTypeCausal;
+  const uint32_t peers = __match_any_sync(0xFFFFFFFFu, idx);
+  const uint32_t strong_lanes = __ballot_sync(0xFFFFFFFFu, strong);
+  if (idx >= 0) {
+    const uint32_t sp = peers & strong_lanes;
+    const int winner = 31 - __clz(sp != 0u ? sp : peers);
+    if (lane == winner && (strong || tab[idx] == 0u)) tab[idx] = code;
+  }
+  __syncwarp();
+}
+
+// Code table of one 128-row Q tile (Q block `qb` in units of 128 rows) of (batch, head) `bh`, built by
+// one warp. Lists in 128-blocks: tab[kvb] = code of KV block kvb. Lists in 64-blocks: four words per
+// 128-wide KV block, tab[4 * kvb + 2 * qh + kh] = code of the 64x64 sub-block (rows 64 * qh ..,
+// columns 64 * kh ..), resolved against the lists of Q blocks 2 * qb and 2 * qb + 1. The table must be
+// zero on entry.
+template <bool B64>
+__device__ __forceinline__ void build_tile_table(const FwdParams& p, int bh, int qb, uint32_t* tab) {
+  const int lane = threadIdx.x & 31;
+  if constexpr (!B64) {
+    if (qb >= p.nq) return;
+    const long long q_index = static_cast<long long>(bh) * p.nq + qb;
+    int n = __ldg(p.kv_num_blocks + q_index);
+    n = max(0, min(n, p.max_blocks));
+    const long long base = q_index * p.max_blocks;
+    for (int i0 = 0; i0 < n; i0 += 32) {
+      const int i = i0 + lane;
+      int kvb = -1;
+      uint32_t code = 0u;
+      if (i < n) code = resolve_entry_blk<kBlock>(p, base, i, qb, kvb);
+      table_put(tab, code != 0u ? kvb : -1, code);
+    }
+  } else {
+#pragma unroll 1
+    for (int qh = 0; qh < 2; ++qh) {
+      const int q64 = 2 * qb + qh;
+      if (q64 >= p.nq_lists) break;
+      const long long q_index = static_cast<long long>(bh) * p.nq_lists + q64;
+      int n = __ldg(p.kv_num_blocks + q_index);
+      n = max(0, min(n, p.max_blocks));
+      const long long base = q_index * p.max_blocks;
+      for (int i0 = 0; i0 < n; i0 += 32) {
+        const int i = i0 + lane;
+        int kv64 = -1;
+        uint32_t code = 0u;
+        if (i < n) code = resolve_entry_blk<64>(p, base, i, q64, kv64);
+        table_put(tab, code != 0u ? 4 * (kv64 >> 1) + 2 * qh + (kv64 & 1) : -1, code);
+      }
+    }
+  }
 }
 
 // Four 0/1 bytes -> 4 bits (byte i -> bit i). Any non-zero byte counts as true.
@@ -166,6 +241,82 @@ __device__ __forceinline__ void build_allow(const FwdParams& p, uint32_t code, i
     allow[0] = allow[1] = allow[2] = allow[3] = 0xFFFFFFFFu;
   }
   if (code & kCodeClip) clip_row(p.seqlen_orig - kvb * kBlock, allow);
+}
+
+// ---- lists in 64x64 blocks: the allow-bits of one row over one 64-wide sub-block (two words) ----
+// Pool layout with 64-blocks: bytes [P, 64, 64] (the reference's torch.bool tensor) or bits [P, 64, 2].
+__device__ __forceinline__ void build_allow_sub64(const FwdParams& p, uint32_t code, int kv64, int r64,
+                                                  uint32_t& a0, uint32_t& a1) {
+  const uint32_t t = code & kCodeTypeMask;
+  if (t == 0u) {
+    a0 = a1 = 0u;
+    return;
+  }
+  if (t == kTypePartial) {
+    const size_t row = static_cast<size_t>(code >> 3) * 64 + r64;
+    if (p.partial_bits != nullptr) {
+      const uint2 v = __ldg(reinterpret_cast<const uint2*>(p.partial_bits) + row);
+      a0 = v.x;
+      a1 = v.y;
+    } else {
+      const uint4* src = reinterpret_cast<const uint4*>(p.partial_bool + row * 64);
+      uint32_t w[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint4 a = __ldg(src + 2 * h);
+        const uint4 b = __ldg(src + 2 * h + 1);
+        w[h] = bytes_to_nibble(a.x) | (bytes_to_nibble(a.y) << 4) | (bytes_to_nibble(a.z) << 8) |
+               (bytes_to_nibble(a.w) << 12) | (bytes_to_nibble(b.x) << 16) | (bytes_to_nibble(b.y) << 20) |
+               (bytes_to_nibble(b.z) << 24) | (bytes_to_nibble(b.w) << 28);
+      }
+      a0 = w[0];
+      a1 = w[1];
+    }
+  } else if (t == kTypeCausal) {   // diagonal sub-block: column c allowed iff c <= r64
+    a0 = r64 >= 31 ? 0xFFFFFFFFu : ((2u << r64) - 1u);
+    a1 = r64 < 32 ? 0u : (r64 >= 63 ? 0xFFFFFFFFu : ((2u << (r64 - 32)) - 1u));
+  } else {
+    a0 = a1 = 0xFFFFFFFFu;
+  }
+  if (code & kCodeClip) {   // keep columns c < limit, 1 <= limit <= 63
+    const int limit = p.seqlen_orig - kv64 * 64;
+    a0 &= limit >= 32 ? 0xFFFFFFFFu : ((1u << limit) - 1u);
+    a1 &= limit <= 32 ? 0u : ((1u << (limit - 32)) - 1u);
+  }
+}
+
+// What a 128x128 tile means for row r, from the tile's code table. Returns 0 when no row of the tile
+// visits KV block kvb, 1 when row r attends all 128 keys, 2 when `allow` (bit c of word c / 32 = key c
+// attended) has to be applied.
+template <bool B64>
+__device__ __forceinline__ int tile_row_allow(const FwdParams& p, const uint32_t* tab, int kvb, int r,
+                                              uint32_t (&allow)[4]) {
+  if constexpr (!B64) {
+    const uint32_t code = tab[kvb];
+    if (code == 0u) return 0;
+    if ((code & kCodeTypeMask) == kTypeFull && !(code & kCodeClip)) return 1;
+    build_allow(p, code, kvb, r, allow);
+    return 2;
+  } else {
+    const uint4 c = reinterpret_cast<const uint4*>(tab)[kvb];
+    if ((c.x | c.y | c.z | c.w) == 0u) return 0;
+    const uint32_t c0 = r < 64 ? c.x : c.z, c1 = r < 64 ? c.y : c.w;
+    if (c0 == static_cast<uint32_t>(kTypeFull) && c1 == static_cast<uint32_t>(kTypeFull)) return 1;
+    build_allow_sub64(p, c0, 2 * kvb, r & 63, allow[0], allow[1]);
+    build_allow_sub64(p, c1, 2 * kvb + 1, r & 63, allow[2], allow[3]);
+    return 2;
+  }
+}
+
+// Does any row of the tile visit KV block kvb?
+template <bool B64>
+__device__ __forceinline__ bool tile_visits(const uint32_t* tab, int kvb) {
+  if constexpr (!B64) {
+    return tab[kvb] != 0u;
+  } else {
+    const uint4 c = reinterpret_cast<const uint4*>(tab)[kvb];
+    return (c.x | c.y | c.z | c.w) != 0u;
+  }
 }
 
 template <bool BF16>
@@ -313,16 +464,16 @@ constexpr float kExp2C2 = 0.24261116981506348f;
 constexpr float kExp2C3 = 0.0551714189350605f;
 constexpr float kRoundMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds to the nearest integer
 
-// P = exp2(s * scale_log2 - M) for the whole row, packed to 16-bit pairs; returns the row sum of
-// the unrounded exponentials. Packed two-wide fp32 arithmetic throughout. Of every kPolyDen
-// element pairs, kPolyNum are evaluated without the MUFU unit: n = round(x) comes out of one
-// fused multiply-add against the rounding constant, 2^(x-n) from the polynomial, and 2^n is added
-// into the exponent field; the other pairs use ex2.approx. That balances the 16/clk MUFU
-// against the FMA pipe. A row with no allowed key so far has M = -inf and every s = -inf: P is
-// then 0 (MUFU lanes) or below 2^-119 (polynomial lanes, wiped by the next rescale).
-template <bool BF16, int kPolyNum, int kPolyDen>
-__device__ __forceinline__ float exp_and_pack(const float (&s)[128], float M, float scale_log2,
-                                              float inv_scale_log2, uint32_t (&pk)[64]) {
+// P = exp2(s * scale_log2 - M) for NS scores of a row (the whole row, or half of it in the two-pass
+// form), packed to 16-bit pairs; returns the sum of the unrounded exponentials. Packed two-wide fp32
+// arithmetic throughout. Of every kPolyDen element pairs, kPolyNum are evaluated without the MUFU
+// unit: n = round(x) comes out of one fused multiply-add against the rounding constant, 2^(x-n) from
+// the polynomial, and 2^n is added into the exponent field; the other pairs use ex2.approx. That
+// balances the 16/clk MUFU against the FMA pipe. A row with no allowed key so far has M = -inf and
+// every s = -inf: P is then 0 (MUFU lanes) or below 2^-119 (polynomial lanes, wiped by the next rescale).
+template <bool BF16, int kPolyNum, int kPolyDen, int NS>
+__device__ __forceinline__ float exp_and_pack_n(const float (&s)[NS], float M, float scale_log2,
+                                                float inv_scale_log2, uint32_t (&pk)[NS / 2]) {
   const float M_use = (M == -INFINITY) ? 0.f : M;
   const float2 c2 = make_float2(scale_log2, scale_log2);
   const float2 negM2 = make_float2(-M_use, -M_use);
@@ -332,7 +483,7 @@ __device__ __forceinline__ float exp_and_pack(const float (&s)[128], float M, fl
   const float s_min = (M_use - 120.f) * inv_scale_log2;  // keeps x >= -120 in the polynomial lanes
   float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
-  for (int j = 0; j < 64; ++j) {
+  for (int j = 0; j < NS / 2; ++j) {
     float2 p2;
     if ((j % kPolyDen) < kPolyNum) {
       const float2 s2 = make_float2(fmaxf(s[2 * j], s_min), fmaxf(s[2 * j + 1], s_min));
@@ -394,44 +545,6 @@ __device__ __forceinline__ float row_max64(const float (&s)[64]) {
   return fmaxf(max3(a, b, c), d);
 }
 
-// exp2(s * scale_log2 - M) for 64 scores -> 32 packed words; returns the sum of the unrounded values.
-// Same arithmetic as exp_and_pack (MUFU ex2 or the FMA-pipe polynomial for kPolyNum of every
-// kPolyDen element pairs).
-template <bool BF16, int kPolyNum, int kPolyDen>
-__device__ __forceinline__ float exp_and_pack64(const float (&s)[64], float M, float scale_log2,
-                                                float inv_scale_log2, uint32_t (&pk)[32]) {
-  const float M_use = (M == -INFINITY) ? 0.f : M;
-  const float2 c2 = make_float2(scale_log2, scale_log2);
-  const float2 negM2 = make_float2(-M_use, -M_use);
-  const float K = kRoundMagic - M_use;
-  const float2 K2 = make_float2(K, K);
-  const float2 minus1 = make_float2(-1.f, -1.f);
-  const float s_min = (M_use - 120.f) * inv_scale_log2;
-  float2 sum2 = make_float2(0.f, 0.f);
-#pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    float2 p2;
-    if ((j % kPolyDen) < kPolyNum) {
-      const float2 s2 = make_float2(fmaxf(s[2 * j], s_min), fmaxf(s[2 * j + 1], s_min));
-      const float2 t2 = __ffma2_rn(s2, c2, K2);
-      const float2 a2 = __ffma2_rn(t2, minus1, K2);
-      const float2 r2 = __ffma2_rn(s2, c2, a2);
-      float2 q2 = __ffma2_rn(r2, make_float2(kExp2C3, kExp2C3), make_float2(kExp2C2, kExp2C2));
-      q2 = __ffma2_rn(q2, r2, make_float2(kExp2C1, kExp2C1));
-      q2 = __ffma2_rn(q2, r2, make_float2(kExp2C0, kExp2C0));
-      p2.x = __int_as_float(__float_as_int(q2.x) + (__float_as_int(t2.x) << 23));
-      p2.y = __int_as_float(__float_as_int(q2.y) + (__float_as_int(t2.y) << 23));
-    } else {
-      const float2 x2 = __ffma2_rn(make_float2(s[2 * j], s[2 * j + 1]), c2, negM2);
-      p2.x = ex2_approx(x2.x);
-      p2.y = ex2_approx(x2.y);
-    }
-    sum2 = __fadd2_rn(sum2, p2);
-    pk[j] = pack2<BF16>(p2.x, p2.y);
-  }
-  return sum2.x + sum2.y;
-}
-
 // Write the packed P row (64 words) to TMEM columns [taddr_row, taddr_row + 64).
 __device__ __forceinline__ void store_p(uint32_t taddr_row, const uint32_t (&pk)[64]) {
 #pragma unroll
@@ -459,15 +572,17 @@ __device__ __forceinline__ void rescale_o(uint32_t taddr_row, float alpha) {
 
 // Final normalisation and store of one output row: O = acc / l (0 when the row attended nothing),
 // LSE = M * ln2 + ln(l) (-inf when the row attended nothing). `zero_row` forces zeros (padding).
+// Only the first p.d_real of the D accumulator columns exist in memory (head_dim 32 is computed as 64).
 template <int D, bool BF16>
 __device__ __forceinline__ void store_output_row(uint32_t taddr_row, bool have_acc,
                                                  const RowState& st, const FwdParams& p,
                                                  long long row_index, bool zero_row) {
   const bool empty = zero_row || !have_acc || st.M == -INFINITY || !(st.l > 0.f);
   const float inv = empty ? 0.f : 1.f / st.l;
-  uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(p.o) + row_index * (D * 2));
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(p.o) + row_index * (p.d_real * 2));
 #pragma unroll
   for (int c = 0; c < D / 32; ++c) {
+    if (32 * c >= p.d_real) break;
     uint32_t r[32];
     if (have_acc) {  // uniform across the CTA's softmax threads of this tile
       tmem_ld32(taddr_row + 32 * c, r);

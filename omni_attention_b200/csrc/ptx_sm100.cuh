@@ -62,9 +62,10 @@ constexpr int kStatusBadIndex = 2;      // a kv_indices entry was outside [0, nu
 
 // Bounded mbarrier wait. `abort_flag` lives in shared memory and is CTA-wide: once any thread
 // has timed out, every later wait in the CTA returns immediately so the CTA drains and exits.
-// Returns true when the barrier phase completed, false when the CTA is aborting.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int32_t* status, int where) {
+// Returns true when the barrier phase completed, false when the CTA is aborting. `limit` is the
+// cycle budget of this wait.
+__device__ __forceinline__ bool mbar_wait_lim(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                              int32_t* status, int where, long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
   const long long t0 = clock64();
@@ -74,12 +75,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (mbar_try_wait(bar, parity)) return true;
     }
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycleLimit) {
+    if (clock64() - t0 > limit) {
       *abort_flag = 1;
       if (status != nullptr) atomicExch(status, kStatusWaitTimeout | (where << 8));
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status, int where) {
+  return mbar_wait_lim(bar, parity, abort_flag, status, where, kWaitCycleLimit);
+}
+
+// Wait used while a CTA that is giving up drains what it has in flight (its own bulk copies, its own
+// MMAs) before it exits: it ignores the abort flag and has a cycle budget of its own.
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity, long long limit) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > limit) return false;
+  }
+  return true;
 }
 
 // Warp-collective wait: lane 0 polls, the other lanes park at the warp barrier. 32 lanes polling the
@@ -108,6 +123,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
       "%4}], [%2];"
       ::"r"(smem_dst),
       "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// The same for a [BH, N, D] view: x along head_dim, y = row inside the (batch, head), z = batch*head.
+// Rows at y >= N and columns at x >= D of the tensor are filled with zeros.
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* tm, uint32_t bar,
+                                            int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+      "%4, %5}], [%2];"
+      ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 
@@ -218,6 +245,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
         "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }

@@ -35,6 +35,9 @@ ABI_SYMBOLS = (
     "omni_attn_fwd_noalloc_sm100",
     "omni_attn_fwd_simple_sm100",
     "omni_attn_pack_partial_masks_sm100",
+    "omni_attn_pack_partial_masks_blk_sm100",
+    "omni_attn_max_seqlen",
+    "omni_attn_set_wait_cycles",
     "omni_attn_build_mask_sm100",
     "omni_attn_bwd_workspace_bytes",
     "omni_attn_bwd_sm100",
@@ -77,6 +80,12 @@ def load_library() -> ctypes.CDLL:
     lib.omni_attn_fwd_ex_sm100.restype = i32
     lib.omni_attn_pack_partial_masks_sm100.argtypes = [vp, vp, i32, vp]
     lib.omni_attn_pack_partial_masks_sm100.restype = i32
+    lib.omni_attn_pack_partial_masks_blk_sm100.argtypes = [vp, vp, i32, i32, vp]
+    lib.omni_attn_pack_partial_masks_blk_sm100.restype = i32
+    lib.omni_attn_max_seqlen.argtypes = [i32, i32, i32]
+    lib.omni_attn_max_seqlen.restype = i32
+    lib.omni_attn_set_wait_cycles.argtypes = [ctypes.c_longlong]
+    lib.omni_attn_set_wait_cycles.restype = None
     lib.omni_attn_build_mask_sm100.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp,
                                                ctypes.c_longlong, vp]
     lib.omni_attn_build_mask_sm100.restype = i32
@@ -109,15 +118,17 @@ def _ptr(t: Optional[Tensor]) -> Optional[int]:
 
 
 def pack_partial_masks(partial_block_masks: Tensor) -> Tensor:
-    """[P, 128, 128] bool (CUDA) -> [P, 128, 4] int32 bit masks, on the current stream."""
+    """[P, blk, blk] bool (CUDA; blk = 128 or 64) -> [P, blk, blk / 32] int32 bit masks, on the current stream."""
     assert partial_block_masks.is_cuda and partial_block_masks.dtype == torch.bool
-    P = partial_block_masks.shape[0]
+    P, blk = partial_block_masks.shape[0], int(partial_block_masks.shape[1])
+    if blk not in (64, 128) or partial_block_masks.shape[2] != blk:
+        raise OmniAttnError(f"partial_block_masks must be [P, 64, 64] or [P, 128, 128], got {tuple(partial_block_masks.shape)}")
     src = partial_block_masks.contiguous()
-    bits = torch.empty(P, 128, 4, dtype=torch.int32, device=src.device)
+    bits = torch.empty(P, blk, blk // 32, dtype=torch.int32, device=src.device)
     if P > 0:
         with torch.cuda.device(src.device):
             stream = torch.cuda.current_stream().cuda_stream
-            _check(load_library().omni_attn_pack_partial_masks_sm100(src.data_ptr(), bits.data_ptr(), P, stream))
+            _check(load_library().omni_attn_pack_partial_masks_blk_sm100(src.data_ptr(), bits.data_ptr(), P, blk, stream))
     return bits
 
 
@@ -155,10 +166,13 @@ def build_block_mask_cuda(modality_positions: Tensor, batch: int, nheads: int, s
     w = bits.to(torch.int64) & 0xFFFFFFFF
     pool = ((w.unsqueeze(-1) >> torch.arange(32, device=device)) & 1).bool().view(need, 128, 128)
     bm = OmniBlockMask(nb, idx, typ, padded, padded, 128, 128, pidx, pool)
+    ready = torch.cuda.Event()
+    ready.record(torch.cuda.current_stream(device))
     for pack in (True, False):
         bm._cache[(str(device), pack)] = {"nb": nb, "idx": idx, "typ": typ, "pidx": pidx,
                                           "pbool": None if pack or need == 0 else pool,
-                                          "pbits": bits if pack and need > 0 else None, "num_partial": need}
+                                          "pbits": bits if pack and need > 0 else None, "num_partial": need,
+                                          "ready": ready, "stream": torch.cuda.current_stream(device).cuda_stream}
     return bm
 
 
@@ -167,6 +181,11 @@ def _device_mask(bm: OmniBlockMask, device: torch.device, pack_bits: bool) -> di
     key = (str(device), pack_bits)
     hit = bm._cache.get(key)
     if hit is not None:
+        # The copies and the pack kernel were enqueued on the stream that was current when the entry
+        # was built; a call on another stream must not run ahead of them.
+        cur = torch.cuda.current_stream(device)
+        if hit.get("ready") is not None and cur.cuda_stream != hit.get("stream"):
+            cur.wait_event(hit["ready"])
         return hit
     cv = lambda t: t.to(device=device, dtype=torch.int32).contiguous()
     d = {"nb": cv(bm.kv_num_blocks), "idx": cv(bm.kv_indices), "typ": cv(bm.block_mask_types),
@@ -180,6 +199,10 @@ def _device_mask(bm: OmniBlockMask, device: torch.device, pack_bits: bool) -> di
                 d["pbits"] = pack_partial_masks(pool)
             else:
                 d["pbool"] = pool
+    with torch.cuda.device(device):
+        d["ready"] = torch.cuda.Event()
+        d["ready"].record(torch.cuda.current_stream(device))
+        d["stream"] = torch.cuda.current_stream(device).cuda_stream
     bm._cache[key] = d
     return d
 
@@ -256,14 +279,17 @@ def _pad_to_block(x: Tensor, block: int) -> Tuple[Tensor, int]:
     return torch.nn.functional.pad(x, (0, 0, 0, rem)), n
 
 
-def _prepare(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMask, scale: Optional[float]):
-    """Shape checks and the conversions that map everything the reference's launchers accept
-    (omni-attn-mma/mma/omni_attn_shared_kv.cu:725-741: head_dim 32/64/128, blocks 64 or 128) onto what
-    the sm_100a kernels are built for (head_dim 64/128, 128x128 blocks):
-      * the sequence is zero-padded to a multiple of 128 (omni_attn_torch.py:1261-1284);
-      * a 64x64-block mask is re-tiled to 128x128 once and cached on the mask object;
-      * head_dim 32 is zero-padded to 64 with the scale kept at 1/sqrt(32): zero columns change
-        neither Q K^T nor the first 32 output columns.
+def _prepare(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMask, scale: Optional[float],
+             for_backward: bool = False):
+    """Shape checks and padding. The forward kernels take everything the reference's launchers accept
+    (omni-attn-mma/mma/omni_attn_shared_kv.cu:725-741: head_dim 32/64/128, blocks 64 or 128) as it is,
+    so all that happens here is the reference wrapper's zero-padding of the sequence to a multiple of
+    the mask's block size (omni_attn_torch.py:1261-1284).
+
+    The backward kernels are built for head_dim 64/128 and 128x128 blocks only; with ``for_backward``
+    the other two forms are mapped onto those on the host: a 64x64-block mask is re-tiled to 128x128
+    once (cached on the mask object) and head_dim 32 is zero-padded to 64 with the scale kept at
+    1/sqrt(32) - zero columns change neither Q K^T nor the first 32 output columns.
     Returns padded contiguous q, k, v, the mask to use, the scale, and the original length / head_dim."""
     B, H, Q, D = query.shape
     if key.shape != (B, H, Q, D) or value.shape != (B, H, Q, D):
@@ -271,23 +297,25 @@ def _prepare(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMas
     if D not in (32, 64, 128):
         raise ValueError(f"Unsupported head_dim={D}. Supported: 32, 64, 128.")
     sizes = (block_mask.Q_BLOCK_SIZE, block_mask.KV_BLOCK_SIZE)
-    if sizes == (64, 64):
-        hit = block_mask._cache.get("retiled128")
-        if hit is None:
-            from .block_mask import retile_block_mask
-
-            hit = retile_block_mask(block_mask, 128)
-            block_mask._cache["retiled128"] = hit
-        block_mask = hit
-    elif sizes != (128, 128):
+    if sizes not in ((64, 64), (128, 128)):
         raise ValueError("Unsupported block size: Q_BLOCK_SIZE and KV_BLOCK_SIZE must both be 64 or both be 128.")
-    if D == 32:
-        if scale is None:
-            scale = 1.0 / math.sqrt(32)
-        query, key, value = (torch.nn.functional.pad(t, (0, 32)) for t in (query, key, value))
-    qp, n_orig = _pad_to_block(query, 128)
-    kp, _ = _pad_to_block(key, 128)
-    vp, _ = _pad_to_block(value, 128)
+    if for_backward:
+        if sizes == (64, 64):
+            hit = block_mask._cache.get("retiled128")
+            if hit is None:
+                from .block_mask import retile_block_mask
+
+                hit = retile_block_mask(block_mask, 128)
+                block_mask._cache["retiled128"] = hit
+            block_mask = hit
+        if D == 32:
+            if scale is None:
+                scale = 1.0 / math.sqrt(32)
+            query, key, value = (torch.nn.functional.pad(t, (0, 32)) for t in (query, key, value))
+    blk = block_mask.Q_BLOCK_SIZE
+    qp, n_orig = _pad_to_block(query, blk)
+    kp, _ = _pad_to_block(key, blk)
+    vp, _ = _pad_to_block(value, blk)
     if qp.shape[2] != block_mask.q_len or kp.shape[2] != block_mask.kv_len:
         raise OmniAttnError(
             f"padded length {qp.shape[2]} does not match the mask's q_len/kv_len ({block_mask.q_len}/{block_mask.kv_len})")
@@ -299,9 +327,8 @@ def omni_attention(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBl
                    check_status: bool = False, softcap: Optional[float] = None) -> Union[Tensor, Tuple[Tensor, Tensor]]:
     """Block-mask attention forward on a B200.
 
-    query/key/value: [B, H, N, D] fp16 or bf16 CUDA tensors with Q_len == KV_len, D in {32, 64, 128}
-    (32 runs zero-padded to 64); ``block_mask`` with 128x128 blocks built for the length padded to 128,
-    or with 64x64 blocks (re-tiled to 128 once). Returns ``out[:, :, :N]`` (and
+    query/key/value: [B, H, N, D] fp16 or bf16 CUDA tensors with Q_len == KV_len, D in {32, 64, 128};
+    ``block_mask`` with 128x128 or 64x64 blocks, built for the length padded to its block size. Returns ``out[:, :, :N]`` (and
     ``lse[:, :, :N]``, natural log, when ``return_lse``). ``softcap`` > 0 applies the Transfusion attention's
     tanh soft-cap to the scaled scores before masking (transfusion_pytorch/transfusion.py:358-364). ``check_status=True`` synchronises and
     raises if the kernel reported a bounded-wait timeout or an out-of-range block index.
@@ -392,7 +419,7 @@ def omni_attention_autograd(query: Tensor, key: Tensor, value: Tensor, block_mas
                             scale: Optional[float] = None, softcap: Optional[float] = None) -> Tensor:
     """``omni_attention`` for training: same inputs and output, differentiable with respect to
     query, key and value (the gradients come from omni_attn_bwd_sm100 / omni_attn_bwd_ex_sm100)."""
-    qp, kp, vp, block_mask, scale, n_orig, d_orig = _prepare(query, key, value, block_mask, scale)
+    qp, kp, vp, block_mask, scale, n_orig, d_orig = _prepare(query, key, value, block_mask, scale, for_backward=True)
     out = _OmniAttentionFn.apply(qp, kp, vp, block_mask, n_orig, scale, softcap if softcap else None)
     return out[:, :, :n_orig, :d_orig]
 

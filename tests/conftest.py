@@ -11,6 +11,9 @@ if ROOT not in sys.path:
 
 GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
 GOLDEN_CASES = ["ref_causal_n256_d64", "ref_fcp_n512_d64", "ref_fcp_n384_d128", "ref_interleaved_n512_d64"]
+# the other block shape (64x64) and head_dim (32) of the reference's launchers
+GOLDEN_CASES_64_32 = ["ref_fcp_n448_d64_blk64", "ref_fcp_n384_d32", "ref_interleaved_n512_d32_blk64",
+                      "ref_fcp_n320_d128_blk64"]
 
 # tolerances of the parity contract: 16-bit outputs atol 2e-2 / rtol 1e-2, log-sum-exp 1e-3
 OUT_ATOL, OUT_RTOL, LSE_ATOL = 2e-2, 1e-2, 1e-3

@@ -82,6 +82,25 @@ def main(ref_dir: str) -> None:
                                       output_file=os.path.join(tmp, "c.pt"), seed=3)
     finish("ref_interleaved_n512_d64", d["Q_fp32"], d["K_fp32"], d["V_fp32"], d["omni_block_mask"], d["dense_mask"])
 
+    # 5.-8. the other block shape and head_dim of the reference's launchers (64x64 blocks, head_dim 32;
+    # omni-attn-mma/mma/omni_attn_shared_kv.cu:725-741), from the same generators
+    d = gdd.generate_fixed_debug_F_C_P_data(B=1, H=2, seq_len=448, head_dim=64, Q_BLOCK_SIZE=64, KV_BLOCK_SIZE=64,
+                                            device="cpu", output_file=os.path.join(tmp, "d.pt"), seed=21)
+    finish("ref_fcp_n448_d64_blk64", d["Q_fp32"], d["K_fp32"], d["V_fp32"], d["omni_block_mask"], d["dense_mask"])
+
+    d = gdd.generate_fixed_debug_F_C_P_data(B=1, H=2, seq_len=384, head_dim=32, device="cpu",
+                                            output_file=os.path.join(tmp, "e.pt"), seed=22)
+    finish("ref_fcp_n384_d32", d["Q_fp32"], d["K_fp32"], d["V_fp32"], d["omni_block_mask"], d["dense_mask"])
+
+    d = gad.generate_interleaved_mask(B=1, H=2, seq_len=512, head_dim=32, Q_BLOCK_SIZE=64, KV_BLOCK_SIZE=64,
+                                      device="cpu", output_file=os.path.join(tmp, "f.pt"), seed=23)
+    finish("ref_interleaved_n512_d32_blk64", d["Q_fp32"], d["K_fp32"], d["V_fp32"], d["omni_block_mask"],
+           d["dense_mask"])
+
+    d = gdd.generate_fixed_debug_F_C_P_data(B=1, H=1, seq_len=320, head_dim=128, Q_BLOCK_SIZE=64, KV_BLOCK_SIZE=64,
+                                            device="cpu", output_file=os.path.join(tmp, "g.pt"), seed=24)
+    finish("ref_fcp_n320_d128_blk64", d["Q_fp32"], d["K_fp32"], d["V_fp32"], d["omni_block_mask"], d["dense_mask"])
+
 
 if __name__ == "__main__":
     here = os.path.dirname(os.path.abspath(__file__))

@@ -65,11 +65,15 @@ def test_argument_validation_codes(fn):
     assert _call(lib, fn, q=None) == E["OMNI_ERR_NULL_POINTER"]
     assert _call(lib, fn, typ=None) == E["OMNI_ERR_NULL_POINTER"]
     assert _call(lib, fn, dtype=2) == E["OMNI_ERR_DTYPE"]
-    assert _call(lib, fn, D=32) == E["OMNI_ERR_HEAD_DIM"]
+    assert _call(lib, fn, D=48) == E["OMNI_ERR_HEAD_DIM"]
     assert _call(lib, fn, D=96) == E["OMNI_ERR_HEAD_DIM"]
-    assert _call(lib, fn, qb=64, kb=64) == E["OMNI_ERR_BLOCK_SIZE"]
+    assert _call(lib, fn, D=256) == E["OMNI_ERR_HEAD_DIM"]
+    assert _call(lib, fn, qb=32, kb=32) == E["OMNI_ERR_BLOCK_SIZE"]
     assert _call(lib, fn, qb=128, kb=64) == E["OMNI_ERR_BLOCK_SIZE"]
+    assert _call(lib, fn, qb=64, kb=128) == E["OMNI_ERR_BLOCK_SIZE"]
     assert _call(lib, fn, N=100) == E["OMNI_ERR_SEQLEN"]
+    assert _call(lib, fn, N=192) == E["OMNI_ERR_SEQLEN"]                   # 192 is a multiple of 64, not of 128
+    assert _call(lib, fn, N=160, qb=64, kb=64) == E["OMNI_ERR_SEQLEN"]
     assert _call(lib, fn, orig=0) == E["OMNI_ERR_SEQLEN"]
     assert _call(lib, fn, orig=129) == E["OMNI_ERR_SEQLEN"]
     assert _call(lib, fn, B=0) == E["OMNI_ERR_SHAPE"]
@@ -78,6 +82,12 @@ def test_argument_validation_codes(fn):
     assert _call(lib, fn, npart=-1) == E["OMNI_ERR_PARTIAL"]
     assert _call(lib, fn, npart=3) == E["OMNI_ERR_PARTIAL"]
     assert _call(lib, fn, N=128 * 1025, orig=128) == E["OMNI_ERR_TOO_LONG"]
+    simple = 1 if fn.endswith("simple_sm100") else 0
+    for D in (32, 64, 128):   # with 64-blocks the tables reach less far; the limit is what the library reports
+        lim = lib.omni_attn_max_seqlen(D, 64, simple)
+        assert 0 < lim < 128 * 1024 and lim % 128 == 0
+        assert _call(lib, fn, N=lim + 64, orig=64, D=D, qb=64, kb=64) == E["OMNI_ERR_TOO_LONG"]
+        assert lib.omni_attn_max_seqlen(D, 128, simple) == 128 * 1024
     base = _call.__defaults__
     buf = (ctypes.c_char * 64)()
     odd = (ctypes.addressof(buf) | 15) - 7  # not 16-byte aligned
@@ -86,9 +96,30 @@ def test_argument_validation_codes(fn):
         assert isinstance(lib.omni_attn_error_string(code), bytes)
 
 
+def test_validation_from_four_threads_at_once():
+    """The entry points hold no unsynchronised first-use state: four host threads making their first
+    calls together all get the documented codes."""
+    import threading
+
+    lib = ops.load_library()
+    E = error_codes()
+    go, got = threading.Barrier(4), [None] * 4
+
+    def work(i):
+        go.wait()
+        got[i] = [_call(lib, q=None), _call(lib, D=96), _call(lib, N=100), lib.omni_attn_max_seqlen(128, 128, 0)]
+
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(4)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert all(g == [E["OMNI_ERR_NULL_POINTER"], E["OMNI_ERR_HEAD_DIM"], E["OMNI_ERR_SEQLEN"], 131072] for g in got)
+
+
 def test_pack_validation():
     lib = ops.load_library()
     E = error_codes()
+    assert lib.omni_attn_pack_partial_masks_blk_sm100(None, None, 2, 32, None) == E["OMNI_ERR_BLOCK_SIZE"]
+    assert lib.omni_attn_pack_partial_masks_blk_sm100(None, None, 2, 64, None) == E["OMNI_ERR_NULL_POINTER"]
     assert lib.omni_attn_pack_partial_masks_sm100(None, None, 0, None) == 0
     assert lib.omni_attn_pack_partial_masks_sm100(None, None, 2, None) == E["OMNI_ERR_NULL_POINTER"]
     assert lib.omni_attn_pack_partial_masks_sm100(None, None, -1, None) == E["OMNI_ERR_PARTIAL"]

@@ -8,7 +8,9 @@ import sys
 import pytest
 import torch
 
-from conftest import GOLDEN_CASES, load_golden
+from conftest import GOLDEN_CASES, GOLDEN_CASES_64_32, load_golden
+
+ALL_GOLDEN = GOLDEN_CASES + GOLDEN_CASES_64_32
 from oracle import omni_oracle as orc
 from oracle import scalar
 
@@ -17,7 +19,7 @@ REF_DIR = os.environ.get("OMNI_REFERENCE_DIR") or os.path.normpath(
     os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference", "omni-attn-mma"))
 
 
-@pytest.mark.parametrize("name", GOLDEN_CASES)
+@pytest.mark.parametrize("name", ALL_GOLDEN)
 def test_dense_mask_matches_reference_expansion(name):
     g = load_golden(name)
     bm = g["bm"]
@@ -28,7 +30,7 @@ def test_dense_mask_matches_reference_expansion(name):
             assert torch.equal(orc.to_dense_mask_slice(bm, b, h), g["dense"][b, h])
 
 
-@pytest.mark.parametrize("name", GOLDEN_CASES)
+@pytest.mark.parametrize("name", ALL_GOLDEN)
 def test_attention_matches_reference_output(name):
     g = load_golden(name)
     out, lse = orc.block_mask_attention(g["q"], g["k"], g["v"], g["bm"])
@@ -37,7 +39,7 @@ def test_attention_matches_reference_output(name):
     assert torch.allclose(lse, g["lse"], atol=2e-6, rtol=1e-6)
 
 
-@pytest.mark.parametrize("name", GOLDEN_CASES)
+@pytest.mark.parametrize("name", ALL_GOLDEN)
 def test_scalar_oracle_matches_reference_output(name):
     g = load_golden(name)
     B, H, N, D = g["q"].shape

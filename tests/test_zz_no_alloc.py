@@ -54,20 +54,53 @@ def _call(fn, q, k, v, bm, dev):
     return out, lse, int(status.item())
 
 
+def test_argument_checks_come_before_anything_else():
+    """A call that is going to be refused is refused before the built-in array is touched: every code of
+    the ordinary entry point comes back from this one too, without a GPU."""
+    lib = ops.load_library()
+    buf = (ctypes.c_char * 4096)()
+    a = (ctypes.addressof(buf) + 15) & ~15
+    call = lambda **kw: lib.omni_attn_fwd_noalloc_sm100(
+        kw.get("q", a), a, a, a, None, a, a, a, a, a, None, 1, 1, kw.get("N", 128), 128, kw.get("D", 64), 128, 128, 1,
+        kw.get("npart", 1), kw.get("dtype", 0), 0.0, None, None)
+    assert call(q=None) == _header_constant("OMNI_ERR_NULL_POINTER")
+    assert call(D=96) == _header_constant("OMNI_ERR_HEAD_DIM")
+    assert call(dtype=5) == _header_constant("OMNI_ERR_DTYPE")
+    assert call(N=100) == _header_constant("OMNI_ERR_SEQLEN")
+    assert call(npart=-2) == _header_constant("OMNI_ERR_PARTIAL")
+
+
+def _device_memory_in_use(dev):
+    free, total = torch.cuda.mem_get_info(dev)
+    return total - free, torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev)
+
+
 @pytest.mark.gpu
 def test_noalloc_entry_matches_existing_entry_on_two_calls_in_a_row(cuda_device):
     lib = ops.load_library()
-    before = torch.cuda.memory_allocated(cuda_device)
-    # the ordinary argument checks still apply
-    buf = (ctypes.c_char * 64)()
-    a = (ctypes.addressof(buf) + 15) & ~15
-    assert lib.omni_attn_fwd_noalloc_sm100(None, a, a, a, None, a, a, a, None, None, None, 1, 1, 128, 128, 64, 128,
-                                           128, 1, 0, 0, 0.0, None, None) == _header_constant("OMNI_ERR_NULL_POINTER")
     for name in ("ref_interleaved_n512_d64", "ref_fcp_n512_d64"):   # second call: other mask, smaller pool
         g = load_golden(name)
         q, k, v = (g[x].to(cuda_device).contiguous() for x in "qkv")
         ref_out, ref_lse, ref_status = _call(lib.omni_attn_fwd_sm100, q, k, v, g["bm"], cuda_device)
         out, lse, status = _call(lib.omni_attn_fwd_noalloc_sm100, q, k, v, g["bm"], cuda_device)
+        # once its first call on the device is behind it, the entry point takes no device memory: neither
+        # the driver's count of bytes in use nor torch's allocator moves across a call
+        # (everything the call needs is allocated by _call's caller side before `before` is read)
+        B, H, N, D = q.shape
+        i32 = lambda t: t.to(device=cuda_device, dtype=torch.int32).contiguous()
+        bm = g["bm"]
+        nb, idx, typ, pidx = i32(bm.kv_num_blocks), i32(bm.kv_indices), i32(bm.block_mask_types), i32(bm.partial_block_mask_indices)
+        pool = bm.partial_block_masks.to(cuda_device).contiguous()
+        o2 = torch.empty_like(q)
+        stream = torch.cuda.current_stream().cuda_stream
+        torch.cuda.synchronize()
+        before = _device_memory_in_use(cuda_device)
+        rc = lib.omni_attn_fwd_noalloc_sm100(q.data_ptr(), k.data_ptr(), v.data_ptr(), o2.data_ptr(), None, nb.data_ptr(),
+                                             idx.data_ptr(), typ.data_ptr(), pidx.data_ptr(), pool.data_ptr(), None, B, H, N, N,
+                                             D, 128, 128, int(idx.shape[3]), int(pool.shape[0]), 0, 0.0, stream, None)
+        torch.cuda.synchronize()
+        assert rc == 0 and _device_memory_in_use(cuda_device) == before
+        assert torch.equal(o2, out)
         assert status == 0 and ref_status == 0
         err = (out.float() - ref_out.float()).abs()
         assert bool((err <= OUT_ATOL + OUT_RTOL * ref_out.float().abs()).all()), f"{name}: max abs err {float(err.max())}"
@@ -92,4 +125,35 @@ def test_noalloc_entry_matches_existing_entry_on_two_calls_in_a_row(cuda_device)
     torch.cuda.synchronize()
     gerr = (out.float().cpu() - g["out"]).abs()
     assert bool((gerr <= OUT_ATOL + OUT_RTOL * g["out"].abs()).all())
-    assert before >= 0
+
+
+@pytest.mark.gpu
+def test_noalloc_entry_at_its_pool_limit(cuda_device):
+    """A byte pool of exactly OMNI_ATTN_NOALLOC_MAX_PARTIAL tiles is the largest the built-in array can
+    bit-pack; the last tile is used. Same result as the ordinary entry point on the byte pool."""
+    from omni_attention_b200.block_mask import BlockMaskType, OmniBlockMask
+
+    lib = ops.load_library()
+    limit = _header_constant("OMNI_ATTN_NOALLOC_MAX_PARTIAL")
+    torch.manual_seed(4)
+    B, H, N, D = 1, 8, 2048, 64
+    nq = N // 128
+    q, k, v = (torch.randn(B, H, N, D).half().to(cuda_device) for _ in range(3))
+    pool = torch.rand(limit, 128, 128) < 0.5
+    pool[:, torch.arange(128), torch.arange(128)] = True          # every row keeps a key in every tile
+    qb = torch.arange(nq).view(nq, 1)
+    pos = torch.arange(nq).view(1, nq)
+    listed = pos <= qb
+    idx = torch.where(listed, pos, 0).to(torch.int32).expand(B, H, nq, nq).contiguous()
+    typ = torch.where(listed, int(BlockMaskType.PARTIAL), 0).to(torch.int32).expand(B, H, nq, nq).contiguous()
+    nb = listed.sum(-1).to(torch.int32).expand(B, H, nq).contiguous()
+    n_entries = B * H * nq * nq
+    pidx = (limit - 1 - torch.arange(n_entries) % limit).to(torch.int32).view(B, H, nq, nq)   # entry 0 -> the last tile
+    pidx = torch.where(typ == int(BlockMaskType.PARTIAL), pidx, torch.full_like(pidx, -1))
+    bm = OmniBlockMask(nb, idx, typ, N, N, 128, 128, pidx, pool)
+    ref_out, ref_lse, ref_status = _call(lib.omni_attn_fwd_sm100, q, k, v, bm, cuda_device)
+    out, lse, status = _call(lib.omni_attn_fwd_noalloc_sm100, q, k, v, bm, cuda_device)
+    assert status == 0 and ref_status == 0
+    err = (out.float() - ref_out.float()).abs()
+    assert bool((err <= OUT_ATOL + OUT_RTOL * ref_out.float().abs()).all()), float(err.max())
+    assert float((lse - ref_lse).abs().max()) <= LSE_ATOL
