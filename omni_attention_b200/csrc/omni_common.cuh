@@ -77,14 +77,32 @@ struct BwdParams {
   float* delta;        // workspace: [BH, N] rowsum(dO * O)
 };
 
-// Resolve entry `i` of the list of (bh, qb) for lists in BLK x BLK blocks. Returns 0 when the entry is
-// not visited.
+// One list entry as stored: KV block id, type code, index into the partial pool.
+struct ListEntry {
+  int kvb;
+  int type;
+  int pidx;
+};
+
+// The three loads of entry `i`, independent of one another (a caller that walks a list issues the
+// loads of many entries before it looks at any of them).
+__device__ __forceinline__ ListEntry load_entry(const FwdParams& p, long long list_base, int i) {
+  ListEntry e;
+  e.kvb = __ldg(p.kv_indices + list_base + i);
+  e.type = __ldg(p.types + list_base + i);
+  e.pidx = -1;
+  if (p.partial_idx != nullptr && (p.partial_bool != nullptr || p.partial_bits != nullptr)) {
+    e.pidx = __ldg(p.partial_idx + list_base + i);
+  }
+  return e;
+}
+
+// What entry `e` of the list of Q block `qb` means, for lists in BLK x BLK blocks: the code of the
+// block, or 0 when the entry is not visited.
 template <int BLK>
-__device__ __forceinline__ uint32_t resolve_entry_blk(const FwdParams& p, long long list_base, int i,
-                                                      int qb, int& kvb_out) {
-  const int kvb = __ldg(p.kv_indices + list_base + i);
-  int t = __ldg(p.types + list_base + i);
-  kvb_out = kvb;
+__device__ __forceinline__ uint32_t resolve_loaded(const FwdParams& p, const ListEntry& e, int qb) {
+  const int kvb = e.kvb;
+  int t = e.type;
   const int n_kv_blocks = BLK == kBlock ? p.nq : p.nq_lists;
   if (kvb < 0 || kvb >= n_kv_blocks) {
     if (p.status != nullptr) atomicCAS(p.status, 0, kStatusBadIndex);
@@ -95,12 +113,8 @@ __device__ __forceinline__ uint32_t resolve_entry_blk(const FwdParams& p, long l
   if (kv_start >= p.seqlen_orig) return 0;
   uint32_t pidx = 0;
   if (t == kTypePartial) {
-    int pi = -1;
-    if (p.partial_idx != nullptr && (p.partial_bool != nullptr || p.partial_bits != nullptr)) {
-      pi = __ldg(p.partial_idx + list_base + i);
-    }
-    if (pi >= 0 && pi < p.num_partial) {
-      pidx = static_cast<uint32_t>(pi);
+    if (e.pidx >= 0 && e.pidx < p.num_partial) {
+      pidx = static_cast<uint32_t>(e.pidx);
     } else {
       t = kTypeCausal;
     }
@@ -116,9 +130,12 @@ __device__ __forceinline__ uint32_t resolve_entry_blk(const FwdParams& p, long l
   return static_cast<uint32_t>(t) | clip | (pidx << 3);
 }
 
+// Resolve entry `i` of the list of (bh, qb), lists in 128-blocks. Returns 0 when the entry is not visited.
 __device__ __forceinline__ uint32_t resolve_entry(const FwdParams& p, long long list_base, int i,
                                                   int qb, int& kvb_out) {
-  return resolve_entry_blk<kBlock>(p, list_base, i, qb, kvb_out);
+  const ListEntry e = load_entry(p, list_base, i);
+  kvb_out = e.kvb;
+  return resolve_loaded<kBlock>(p, e, qb);
 }
 
 // Warp-collective write of one resolved entry per lane into a code table (`idx` < 0: this lane has
@@ -146,39 +163,49 @@ __device__ __forceinline__ void table_put(uint32_t* tab, int idx, uint32_t code)
 // one warp. Lists in 128-blocks: tab[kvb] = code of KV block kvb. Lists in 64-blocks: four words per
 // 128-wide KV block, tab[4 * kvb + 2 * qh + kh] = code of the 64x64 sub-block (rows 64 * qh ..,
 // columns 64 * kh ..), resolved against the lists of Q blocks 2 * qb and 2 * qb + 1. The table must be
-// zero on entry.
+// zero on entry. A list is taken 128 entries at a time: all their loads first, then the writes in
+// list order, so that a long list costs one memory latency per 128 entries and not one per 32.
+template <int BLK>
+__device__ __forceinline__ void put_list(const FwdParams& p, long long q_index, int q_block, uint32_t* tab,
+                                         int sub_row) {
+  const int lane = threadIdx.x & 31;
+  int n = __ldg(p.kv_num_blocks + q_index);
+  n = max(0, min(n, p.max_blocks));
+  const long long base = q_index * p.max_blocks;
+  constexpr int kBatch = 4;
+  for (int i0 = 0; i0 < n; i0 += 32 * kBatch) {
+    ListEntry ent[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int i = i0 + 32 * j + lane;
+      ent[j].kvb = -1;
+      ent[j].type = 0;
+      ent[j].pidx = -1;
+      if (i < n) ent[j] = load_entry(p, base, i);
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (i0 + 32 * j >= n) break;   // the same for every lane
+      const int i = i0 + 32 * j + lane;
+      const uint32_t code = i < n ? resolve_loaded<BLK>(p, ent[j], q_block) : 0u;
+      int idx = -1;
+      if (code != 0u) idx = BLK == kBlock ? ent[j].kvb : 4 * (ent[j].kvb >> 1) + 2 * sub_row + (ent[j].kvb & 1);
+      table_put(tab, idx, code);
+    }
+  }
+}
+
 template <bool B64>
 __device__ __forceinline__ void build_tile_table(const FwdParams& p, int bh, int qb, uint32_t* tab) {
-  const int lane = threadIdx.x & 31;
   if constexpr (!B64) {
     if (qb >= p.nq) return;
-    const long long q_index = static_cast<long long>(bh) * p.nq + qb;
-    int n = __ldg(p.kv_num_blocks + q_index);
-    n = max(0, min(n, p.max_blocks));
-    const long long base = q_index * p.max_blocks;
-    for (int i0 = 0; i0 < n; i0 += 32) {
-      const int i = i0 + lane;
-      int kvb = -1;
-      uint32_t code = 0u;
-      if (i < n) code = resolve_entry_blk<kBlock>(p, base, i, qb, kvb);
-      table_put(tab, code != 0u ? kvb : -1, code);
-    }
+    put_list<kBlock>(p, static_cast<long long>(bh) * p.nq + qb, qb, tab, 0);
   } else {
 #pragma unroll 1
     for (int qh = 0; qh < 2; ++qh) {
       const int q64 = 2 * qb + qh;
       if (q64 >= p.nq_lists) break;
-      const long long q_index = static_cast<long long>(bh) * p.nq_lists + q64;
-      int n = __ldg(p.kv_num_blocks + q_index);
-      n = max(0, min(n, p.max_blocks));
-      const long long base = q_index * p.max_blocks;
-      for (int i0 = 0; i0 < n; i0 += 32) {
-        const int i = i0 + lane;
-        int kv64 = -1;
-        uint32_t code = 0u;
-        if (i < n) code = resolve_entry_blk<64>(p, base, i, q64, kv64);
-        table_put(tab, code != 0u ? 4 * (kv64 >> 1) + 2 * qh + (kv64 & 1) : -1, code);
-      }
+      put_list<64>(p, static_cast<long long>(bh) * p.nq_lists + q64, q64, tab, qh);
     }
   }
 }
@@ -285,20 +312,20 @@ __device__ __forceinline__ void build_allow_sub64(const FwdParams& p, uint32_t c
   }
 }
 
-// What a 128x128 tile means for row r, from the tile's code table. Returns 0 when no row of the tile
-// visits KV block kvb, 1 when row r attends all 128 keys, 2 when `allow` (bit c of word c / 32 = key c
-// attended) has to be applied.
+// What a 128x128 tile means for row r, from the tile's code table (`tab` is the table's shared-memory
+// address). Returns 0 when no row of the tile visits KV block kvb, 1 when row r attends all 128 keys,
+// 2 when `allow` (bit c of word c / 32 = key c attended) has to be applied.
 template <bool B64>
-__device__ __forceinline__ int tile_row_allow(const FwdParams& p, const uint32_t* tab, int kvb, int r,
+__device__ __forceinline__ int tile_row_allow(const FwdParams& p, uint32_t tab, int kvb, int r,
                                               uint32_t (&allow)[4]) {
   if constexpr (!B64) {
-    const uint32_t code = tab[kvb];
+    const uint32_t code = lds_u32(tab + 4 * kvb);
     if (code == 0u) return 0;
     if ((code & kCodeTypeMask) == kTypeFull && !(code & kCodeClip)) return 1;
     build_allow(p, code, kvb, r, allow);
     return 2;
   } else {
-    const uint4 c = reinterpret_cast<const uint4*>(tab)[kvb];
+    const uint4 c = lds_v4(tab + 16 * kvb);
     if ((c.x | c.y | c.z | c.w) == 0u) return 0;
     const uint32_t c0 = r < 64 ? c.x : c.z, c1 = r < 64 ? c.y : c.w;
     if (c0 == static_cast<uint32_t>(kTypeFull) && c1 == static_cast<uint32_t>(kTypeFull)) return 1;
@@ -310,11 +337,11 @@ __device__ __forceinline__ int tile_row_allow(const FwdParams& p, const uint32_t
 
 // Does any row of the tile visit KV block kvb?
 template <bool B64>
-__device__ __forceinline__ bool tile_visits(const uint32_t* tab, int kvb) {
+__device__ __forceinline__ bool tile_visits(uint32_t tab, int kvb) {
   if constexpr (!B64) {
-    return tab[kvb] != 0u;
+    return lds_u32(tab + 4 * kvb) != 0u;
   } else {
-    const uint4 c = reinterpret_cast<const uint4*>(tab)[kvb];
+    const uint4 c = lds_v4(tab + 16 * kvb);
     return (c.x | c.y | c.z | c.w) != 0u;
   }
 }

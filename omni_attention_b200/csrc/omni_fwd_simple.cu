@@ -76,6 +76,7 @@ omni_fwd_simple_kernel(const __grid_constant__ CUtensorMap tmQ,
   __syncthreads();
   if (warp == 1) build_tile_table<B64>(p, bh, qb, tab);
   __syncthreads();
+  const uint32_t tab_addr = smem_u32(tab);
 
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
@@ -101,7 +102,7 @@ omni_fwd_simple_kernel(const __grid_constant__ CUtensorMap tmQ,
   uint32_t ph = 0;
 
   for (int kvb = 0; kvb < p.nq; ++kvb) {
-    if (!tile_visits<B64>(tab, kvb)) continue;   // identical in every thread
+    if (!tile_visits<B64>(tab_addr, kvb)) continue;   // identical in every thread
 
     if (tid == 0) {
       const int y = kvb * kBlock;
@@ -126,7 +127,7 @@ omni_fwd_simple_kernel(const __grid_constant__ CUtensorMap tmQ,
 
     // Fetch this row's allow-bits while the MMA runs.
     uint32_t allow[4];
-    const bool masked = tile_row_allow<B64>(p, tab, kvb, tid, allow) == 2;
+    const bool masked = tile_row_allow<B64>(p, tab_addr, kvb, tid, allow) == 2;
 
     mbar_wait(bar_s, ph, abort_flag, p.status, 3);
     tc_fence_after();

@@ -3,26 +3,27 @@
 // One CTA per SM stays resident and works through a list of UNITS; a unit is a PAIR of adjacent 128-row
 // Q tiles (tile A = rows 256j .., tile B = rows 256j + 128 ..) of one (batch, head). For a unit the CTA
 // walks the union of the two tiles' KV block lists once, so every K/V tile staged in shared memory
-// feeds up to two Q tiles. Roles (512 threads = 4 warpgroups):
+// feeds up to two Q tiles. Roles (384 threads = 3 warpgroups):
 //   warps 0-3    softmax group of tile A   (thread = one query row, TMEM lane = row)
 //   warps 4-7    softmax group of tile B
 //   warp  8      TMA producer: Q tiles of a unit, then K,V tiles through a ring of shared-memory stages
 //   warp  9      MMA issuer: tcgen05.mma for S = Q K^T (smem x smem) and O += P V (TMEM x smem)
-//   warp  10     idle
+//   warp  10     idle (completes the third warpgroup, which hands its registers to the softmax groups
+//                with setmaxnreg: 208 registers per softmax thread, 88 elsewhere)
 //   warp  11     unit scheduler: takes the next unit (atomic counter in caller-provided scratch, or a
 //                fixed boustrophedon assignment without scratch), resolves the block lists into
 //                per-KV-block code tables and one ascending schedule, double buffered, one unit ahead
-//   warps 12-15  output group: when a tile's last P*V of a unit has retired it reads O out of TMEM,
-//                normalises, casts and stores it (and the log-sum-exp), while the softmax groups are
-//                already at work on the next unit
-// setmaxnreg moves registers from warps 8-15 to the softmax groups.
+// A separate output warpgroup (a fourth group of 128 threads that reads O out of TMEM, normalises and
+// stores while the softmax groups go on to the next unit) was built and measured: 0.555 ms against
+// 0.537 ms on the 8K-token workload, because 512 threads leave the softmax groups 192 registers instead
+// of 208 and put a third warp on every scheduler; the softmax groups therefore write the output themselves.
 // TMEM (512 columns): S_A [0,128) S_B [128,256) O_A [256,256+D) O_B [256+D,256+2D). P (16-bit) is
 // written over the first 64 columns of its S.
 //
 // Everything that is per-unit overhead in a one-unit-per-CTA kernel overlaps here with the
 // neighbouring units: table building (scheduler warp), the Q/K/V loads of the next unit (the ring never
-// drains; Q is reloaded as soon as the last S of the unit has been issued), the output of the previous
-// unit (output group).
+// drains; Q is reloaded as soon as the last S of the unit has been issued), and the first S MMAs of
+// the next unit run while the softmax groups still normalise and store the previous output.
 //
 // Per tile the MMA order is PV(e), S(e+1), PV(e+1) ...; the two tiles' batches alternate in the
 // tensor pipe, so while one tile's softmax runs on the CUDA cores the pipe works on the other tile.
@@ -52,7 +53,7 @@ namespace omni {
 
 // Header of a unit-table slot. The slot holds, in this order: the two code tables (tile A, tile B;
 // one word per KV block, four with lists in 64-blocks), the schedule (KV blocks visited by either
-// tile, ascending, 16-bit) and this header.
+// tile, ascending, 16-bit: block | kSchedA | kSchedB) and this header.
 struct UnitHeader {
   int n_sched;   // entries in the schedule; -1 = no more units
   int cnt[2];    // blocks visited by tile A / tile B
@@ -87,48 +88,32 @@ struct WsCfg {
   //    a time), so that the scores and the packed P are never live together and nothing spills.
   //  * D=64: one pass with the whole row in registers, a quarter of the exponentials evaluated by a
   //    polynomial on the FMA pipe (the MMAs are half as long, MUFU is the scarcer unit).
-#ifdef OMNI_WS_TWOPASS64
-  static constexpr bool kTwoPass = true;
-#else
   static constexpr bool kTwoPass = (D == 128);
-#endif
-#ifdef OMNI_WS_POLY_NUM128
-  static constexpr int kPolyNum = (D == 128) ? OMNI_WS_POLY_NUM128 : 1;
-  static constexpr int kPolyDen = (D == 128) ? OMNI_WS_POLY_DEN128 : 4;
-#else
   static constexpr int kPolyNum = (D == 128) ? 0 : 1;   // element pairs per group of kPolyDen on the FMA pipe
   static constexpr int kPolyDen = (D == 128) ? 1 : 4;
-#endif
   // q_full[2] q_free ring_full[S] ring_empty[S] s_full[2] p_ready[2] done[2] o_free[2] tab_full[2]
-  // tab_empty[2] near_end row_state[2] row_state_free[2] drained
-  static constexpr int kNumBars = 3 + 2 * kStages + 13 + 5;
-  static constexpr int kRowStateBytes = 2 * kBlock * 8;   // (M, l) of every row of the two tiles
+  // tab_empty[2] near_end drained
+  static constexpr int kNumBars = 3 + 2 * kStages + 13 + 1;
   static constexpr int kBarBytes = (8 * kNumBars + 64 + 15) & ~15;   // barriers + a few control words; the table slots
                                                                      // behind them stay 16-byte aligned
-  static constexpr int kFixedBytes = (2 + kStages) * kTileBytes + kRowStateBytes + kBarBytes;
+  static constexpr int kFixedBytes = (2 + kStages) * kTileBytes + kBarBytes + 1024;   // + alignment slack
 };
 
-constexpr int kWsThreads = 512;
-// Register split made with setmaxnreg. The kernel is compiled for 128 registers per thread (the most
-// 512 threads can have); the increase of the two softmax warpgroups must be covered by the decrease
-// of the other two, or setmaxnreg.inc waits forever.
-constexpr int kLaunchRegs = 128;
-#ifndef OMNI_WS_REGS128_S
-#define OMNI_WS_REGS128_S 192
-#define OMNI_WS_REGS128_R 88
-#endif
-#ifndef OMNI_WS_REGS64_S
-#define OMNI_WS_REGS64_S 208
-#define OMNI_WS_REGS64_R 64
-#endif
-template <int D>
-struct WsRegs {
-  static constexpr int kSoftmax = D == 128 ? OMNI_WS_REGS128_S : OMNI_WS_REGS64_S;   // warps 0-7
-  static constexpr int kRole = D == 128 ? OMNI_WS_REGS128_R : OMNI_WS_REGS64_R;      // warps 8-11
-  static constexpr int kOutput = 4 * kLaunchRegs - 2 * kSoftmax - kRole;              // warps 12-15
-  static_assert(kSoftmax % 8 == 0 && kRole % 8 == 0 && kOutput % 8 == 0 && kRole >= 24 && kOutput >= 24,
-                "setmaxnreg counts are multiples of 8, at least 24, and add up to the launch allocation");
-};
+constexpr int kWsThreads = 384;
+// Register split made with setmaxnreg. The kernel is compiled for 168 registers per thread (the most
+// 384 threads can have); the increase of the two softmax warpgroups must be covered by the decrease
+// of the third one, or setmaxnreg.inc waits forever.
+constexpr int kLaunchRegs = 168;
+constexpr int kSoftmaxRegs = 208;   // warps 0-7
+constexpr int kOtherRegs = 88;      // warps 8-11
+static_assert(2 * kSoftmaxRegs + kOtherRegs <= 3 * kLaunchRegs, "setmaxnreg split exceeds the launch allocation");
+static_assert(kSoftmaxRegs % 8 == 0 && kOtherRegs % 8 == 0, "setmaxnreg counts are multiples of 8");
+
+// A schedule entry: KV block (128 keys) in the low bits, and which of the two tiles visit it.
+constexpr int kSchedBlockMask = 0x3FFF;
+constexpr int kSchedA = 0x4000;
+constexpr int kSchedB = 0x8000;
+static_assert(kMaxKvBlocks <= kSchedBlockMask + 1, "schedule entries are 16 bits");
 
 constexpr float kLazyRescaleLog2 = 8.f;
 // The scheduler warp takes the next unit only when the producer is this many KV blocks from the end
@@ -176,18 +161,17 @@ __global__ void __launch_bounds__(kWsThreads, 1)
 omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
   using Cfg = WsCfg<D>;
-  extern __shared__ __align__(1024) uint8_t smem[];
-  if ((smem_u32(smem) & 1023u) != 0u) {   // the swizzled tiles need 1024-byte alignment
-    if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, kStatusWaitTimeout | (1 << 8));
-    return;
-  }
+  // The swizzled tiles need 1024-byte alignment: the launch asks for 1 KB more than the layout takes and
+  // the base is rounded up here. (Declaring the array 1024-byte aligned instead, which saves the spare
+  // kilobyte, was measured 8 % slower on the 8K-token workload with an otherwise identical kernel.)
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
   // ---- shared memory carve-up ----------------------------------------------------------------
   const uint32_t sQ0 = smem_u32(smem);                          // Q tile A, then Q tile B
   const uint32_t sRing = sQ0 + 2 * Cfg::kTileBytes;             // kStages K/V tiles
   uint8_t* after_tiles = smem + (2 + Cfg::kStages) * Cfg::kTileBytes;
-  float2* row_state = reinterpret_cast<float2*>(after_tiles);   // [2][128] (M, l) handed to the output group
-  uint64_t* bars = reinterpret_cast<uint64_t*>(after_tiles + Cfg::kRowStateBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(after_tiles);
   const uint32_t bar_q = smem_u32(bars + 0);                    // [2] Q tile landed
   const uint32_t bar_qfree = smem_u32(bars + 2);                // every S of the unit has been issued and is done
   const uint32_t bar_full = smem_u32(bars + 3);                 // [kStages] ring entry landed
@@ -197,15 +181,13 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t bar_done = bar_p + 16;                         // [2] all MMAs of the tile in this unit complete
   const uint32_t bar_ofree = bar_done + 16;                     // [2] O of the unit read out of TMEM (128 arrivals)
   const uint32_t bar_tfull = bar_ofree + 16;                    // [2] unit table written
-  const uint32_t bar_tempty = bar_tfull + 16;                   // [2] unit table no longer needed (14 arrivals)
+  const uint32_t bar_tempty = bar_tfull + 16;                   // [2] unit table no longer needed (10 arrivals)
   const uint32_t bar_near = bar_tempty + 16;                    // the producer is within a few blocks of the unit's end
-  const uint32_t bar_rs = bar_near + 8;                         // [2] row states of the tile written (128 arrivals)
-  const uint32_t bar_rsfree = bar_rs + 16;                      // [2] row states read (128 arrivals)
-  const uint32_t bar_drain = bar_rsfree + 16;                   // every MMA issued by this CTA has retired
+  const uint32_t bar_drain = bar_near + 8;                      // every MMA issued by this CTA has retired
   int* misc = reinterpret_cast<int*>(bars + Cfg::kNumBars);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 0);
   volatile int* abort_flag = misc + 1;
-  uint8_t* slot_base = after_tiles + Cfg::kRowStateBytes + Cfg::kBarBytes;
+  uint8_t* slot_base = after_tiles + Cfg::kBarBytes;
   const int slot_bytes = ws_slot_bytes(p.nq, B64);
   auto slot = [&](int k) -> UnitSlot {
     uint8_t* b = slot_base + (k & 1) * slot_bytes;
@@ -239,9 +221,7 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(bar_done + 8 * g, 1);
       mbar_init(bar_ofree + 8 * g, 128);
       mbar_init(bar_tfull + 8 * g, 1);
-      mbar_init(bar_tempty + 8 * g, 14);
-      mbar_init(bar_rs + 8 * g, 128);
-      mbar_init(bar_rsfree + 8 * g, 128);
+      mbar_init(bar_tempty + 8 * g, 10);
     }
     mbar_init(bar_near, 1);
     mbar_init(bar_drain, 1);
@@ -275,16 +255,9 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_wait_lim(bar_tfull + 8 * (k & 1), (k >> 1) & 1, abort_flag, p.status, where, wait_lim);
     return slot(k);
   };
-  // Warp-collective form for the 128-thread groups: one lane polls (32 lanes polling the same
-  // mbarrier cost shared-memory bandwidth that the tensor pipe's operand reads need).
-  auto wait_warp = [&](uint32_t bar, uint32_t parity, int where) {
-    if (lane == 0) mbar_wait_lim(bar, parity, abort_flag, p.status, where, wait_lim);
-    __syncwarp();
-  };
-
   if (warp < 8) {
     // =========================== softmax groups =================================================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WsRegs<D>::kSoftmax));
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
     const int g = warp >> 2;                       // 0 = tile A, 1 = tile B
     const int r = tid & 127;                       // row inside the tile = TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -293,25 +266,27 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t my_bar_s = bar_s + 8 * g;
     const uint32_t my_bar_p = bar_p + 8 * g;
     int n_tiles = 0;   // S tiles consumed so far over all units = phase count of the S and P barriers
-    int n_units = 0;   // units in which this tile had work = phase count of the row-state barriers
+    int n_units = 0;   // units in which this tile had work = phase count of its done barrier
 
     for (int k = 0;; ++k) {
       const UnitSlot T = wait_table(k, 10 + g);
       const int n_sched = T.hdr->n_sched;
       if (n_sched < 0) break;
-      const uint32_t* tab = T.tab[g];
+      const uint32_t tab = smem_u32(T.tab[g]);
+      const uint32_t sched = smem_u32(T.sched);
       const int my_cnt = T.hdr->cnt[g];
+      const int unit_bh = T.hdr->bh, unit_pair = T.hdr->pair;
 
       RowState st{-INFINITY, 0.f};
       int cnt = 0;
       for (int e = 0; e < n_sched && cnt < my_cnt; ++e) {
-        const int kvb = T.sched[e];
+        const int entry = lds_u16(sched + 2 * e);
+        if ((entry & (g == 0 ? kSchedA : kSchedB)) == 0) continue;
+        const int kvb = entry & kSchedBlockMask;
         uint32_t allow[4];
-        const int kind = tile_row_allow<B64>(p, tab, kvb, r, allow);
-        if (kind == 0) continue;
-        const bool masked = kind == 2;
+        const bool masked = tile_row_allow<B64>(p, tab, kvb, r, allow) == 2;
 
-        wait_warp(my_bar_s, n_tiles & 1, 12 + g);
+        mbar_wait_lim(my_bar_s, n_tiles & 1, abort_flag, p.status, 12 + g, wait_lim);
         tc_fence_after();
 
         if constexpr (Cfg::kTwoPass) {
@@ -369,74 +344,45 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         ++n_tiles;
       }
 
-      // ---- hand the row's softmax state to the output group and go on to the next unit -----------
-      if (my_cnt > 0) {
-        if (n_units > 0) wait_warp(bar_rsfree + 8 * g, (n_units - 1) & 1, 14 + g);
-        row_state[g * kBlock + r] = make_float2(st.M, st.l);
-        mbar_arrive(bar_rs + 8 * g);
-        ++n_units;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * (k & 1));
-    }
-  } else if (warp >= 12) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WsRegs<D>::kOutput));
-    {
-      // =========================== output group ===================================================
-      const int r = tid & 127;
-      const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-      int n_units[2] = {0, 0};   // units in which the tile had work = phase count of its done / row-state barriers
-      for (int k = 0;; ++k) {
-        const UnitSlot T = wait_table(k, 50);
-        if (T.hdr->n_sched < 0) break;
-        const int bh = T.hdr->bh;
-        const int pair = T.hdr->pair;
-        const int cnt_g[2] = {T.hdr->cnt[0], T.hdr->cnt[1]};
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tempty + 8 * (k & 1));   // everything needed from the table is in registers
+      {
+        // ---- output of the unit by the softmax group itself: O out of TMEM chunk by chunk, normalise,
+        // store; O is handed back to the MMA issuer as soon as the last chunk has been read ----------
+        if (my_cnt > 0) {
+          mbar_wait_lim(bar_done + 8 * g, n_units & 1, abort_flag, p.status, 14 + g, wait_lim);
+          tc_fence_after();
+          ++n_units;
+        }
+        const int q_abs = (2 * unit_pair + g) * kBlock + r;
+        const bool have_row = q_abs < p.N;
+        const bool empty = my_cnt == 0 || q_abs >= p.seqlen_orig || st.M == -INFINITY || !(st.l > 0.f);
+        const float inv = empty ? 0.f : 1.f / st.l;
+        const long long row = static_cast<long long>(unit_bh) * p.N + q_abs;
+        char* dst = static_cast<char*>(p.o) + row * (p.d_real * 2);
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          const int q_abs = (2 * pair + g) * kBlock + r;
-          const bool have_row = q_abs < p.N;
-          const bool have_acc = cnt_g[g] > 0;
-          float2 ml = make_float2(-INFINITY, 0.f);
-          if (have_acc) {
-            const uint32_t ph = n_units[g] & 1;
-            wait_warp(bar_rs + 8 * g, ph, 51 + g);
-            ml = row_state[g * kBlock + r];
-            mbar_arrive(bar_rsfree + 8 * g);
-            wait_warp(bar_done + 8 * g, ph, 53 + g);
-            tc_fence_after();
-            ++n_units[g];
-          }
-          const bool empty = !have_acc || q_abs >= p.seqlen_orig || ml.x == -INFINITY || !(ml.y > 0.f);
-          const float inv = empty ? 0.f : 1.f / ml.y;
-          const long long row = static_cast<long long>(bh) * p.N + q_abs;
-          char* dst = static_cast<char*>(p.o) + row * (p.d_real * 2);
-          const uint32_t tO = tmem_base + 256 + D * g + lane_base;
-#pragma unroll
-          for (int c = 0; c < D / 16; ++c) {
-            uint32_t rr[16];
-            if (have_acc) {   // uniform over the group
-              tmem_ld16(tO + 16 * c, rr);
-              tc_wait_ld();
-              if (c == D / 16 - 1) {
-                tc_fence_before();
-                mbar_arrive(bar_ofree + 8 * g);   // the next unit may overwrite O now
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) rr[j] = 0u;
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t rr[32];
+          if (my_cnt > 0) {   // uniform over the group
+            tmem_ld32(tO + 32 * c, rr);
+            tc_wait_ld();
+            if (c == D / 32 - 1) {
+              tc_fence_before();
+              mbar_arrive(bar_ofree + 8 * g);   // the next unit may overwrite O now
             }
-            if (have_row && 16 * c < p.d_real) {   // 16 elements = 32 bytes = one full sector per store
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) rr[j] = 0u;
+          }
+          if (have_row && 32 * c < p.d_real) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {   // 16 elements = 32 bytes = one full sector per store
               uint32_t w[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                const float a = empty ? 0.f : __uint_as_float(rr[2 * j]) * inv;
-                const float b = empty ? 0.f : __uint_as_float(rr[2 * j + 1]) * inv;
+                const float a = empty ? 0.f : __uint_as_float(rr[16 * h + 2 * j]) * inv;
+                const float b = empty ? 0.f : __uint_as_float(rr[16 * h + 2 * j + 1]) * inv;
                 w[j] = pack2<BF16>(a, b);
               }
-              char* d32 = dst + 32 * c;
+              char* d32 = dst + 64 * c + 32 * h;
               if (p.o_aligned32) {
                 asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(d32), "r"(w[0]), "r"(w[1]),
                              "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
@@ -447,14 +393,16 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               }
             }
           }
-          if (have_row && p.lse != nullptr) {
-            p.lse[row] = empty ? -INFINITY : fmaf(ml.x, 0.6931471805599453f, __logf(ml.y));
-          }
+        }
+        if (have_row && p.lse != nullptr) {
+          p.lse[row] = empty ? -INFINITY : fmaf(st.M, 0.6931471805599453f, __logf(st.l));
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * (k & 1));
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WsRegs<D>::kRole));
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
     if (warp == 8) {
       // =========================== TMA producer ===================================================
       if (lane == 0) {
@@ -489,7 +437,7 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           bool alive = true;
           for (int e = 0; e < n_sched && alive; ++e) {
             if (e == near_at) mbar_arrive(bar_near);
-            const int y = static_cast<int>(T.sched[e]) * kBlock;
+            const int y = (static_cast<int>(T.sched[e]) & kSchedBlockMask) * kBlock;
 #pragma unroll
             for (int kv = 0; kv < 2; ++kv, ++fill) {
               const int s = fill % Cfg::kStages;
@@ -524,50 +472,46 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     } else if (warp == 9) {
       // =========================== MMA issuer =====================================================
+      // One thread feeds the tensor pipe, and it shares its scheduler with two softmax warps: every
+      // instruction it does not need is pipe time. Descriptors are advanced as 32-bit low words (the
+      // high word is one constant), accumulate flags are compile-time constants, what a schedule entry
+      // means for the two tiles is in the entry itself, and a look ahead at a barrier is a
+      // non-blocking test.
       if (lane == 0) {
         const uint32_t tS[2] = {tmem_base, tmem_base + 128};
         const uint32_t tO[2] = {tmem_base + 256, tmem_base + 256 + D};
-        // UMMA descriptors: "base + constant" in the start-address field (16-byte units).
-        const uint64_t k_desc0 = umma_smem_desc_sw128(sRing, 16, 1024);                 // K-major view of a ring slot
-        const uint64_t v_desc0 = umma_smem_desc_sw128(sRing, Cfg::kChunkBytes, 1024);   // MN-major view (V)
+        constexpr uint32_t desc_hi = umma_desc_hi_sw128(1024);
+        const uint32_t k_lo0 = umma_desc_lo(sRing, 16);                 // K-major view of ring entry 0
+        const uint32_t v_lo0 = umma_desc_lo(sRing, Cfg::kChunkBytes);   // MN-major view (V)
+        const uint32_t q_lo[2] = {umma_desc_lo(sQ0, 16), umma_desc_lo(sQ0 + Cfg::kTileBytes, 16)};
         constexpr uint32_t kSlotStep = Cfg::kTileBytes >> 4;
         constexpr uint32_t kChunkStep = Cfg::kChunkBytes >> 4;
-        const uint64_t q_desc[2] = {umma_smem_desc_sw128(sQ0, 16, 1024),
-                                    umma_smem_desc_sw128(sQ0 + Cfg::kTileBytes, 16, 1024)};
-        int fbase = 0;             // ring index of K(0) of the current unit
-        int n_p[2] = {0, 0};       // P tiles consumed so far over all units = phase count of the P barriers
-        int n_q[2] = {0, 0};       // Q tile loads consumed so far
-        int n_units[2] = {0, 0};   // units in which the tile had work = phase count of its done / O-free barriers
+        uint32_t fbase = 0;             // ring index of K(0) of the current unit
+        uint32_t n_p[2] = {0, 0};       // P tiles consumed so far over all units = phase count of the P barriers
+        uint32_t n_q[2] = {0, 0};       // Q tile loads consumed so far
+        uint32_t n_units[2] = {0, 0};   // units in which the tile had work = phase count of its done / O-free barriers
         bool issued_any = false;
-        bool alive = true;         // false once a wait has given up: issue no further MMAs
+        bool alive = true;              // false once a wait has given up: issue no further MMAs
 
         for (int k = 0;; ++k) {
-          const UnitSlot T = wait_table(k, 30);
+          mbar_wait_lim(bar_tfull + 8 * (k & 1), (k >> 1) & 1, abort_flag, p.status, 30, wait_lim);
+          const UnitSlot T = slot(k);
           const int n_sched = T.hdr->n_sched;
           if (n_sched < 0 || !alive) break;
           const int cnt_g[2] = {T.hdr->cnt[0], T.hdr->cnt[1]};
-          const uint32_t* tabA = T.tab[0];
-          const uint32_t* tabB = T.tab[1];
+          const uint32_t sched = smem_u32(T.sched);
           bool q_ready[2] = {false, false};
           int n_pv[2] = {0, 0};    // P*V batches issued in this unit
 
-          auto slot_of = [&](int f) { return static_cast<uint32_t>((fbase + f) % Cfg::kStages); };
-          auto wait_full = [&](int f) {
-            alive &= mbar_wait_lim(bar_full + 8 * ((fbase + f) % Cfg::kStages), ((fbase + f) / Cfg::kStages) & 1,
-                                   abort_flag, p.status, 31, wait_lim);
+          auto full_bar = [&](uint32_t f) { return bar_full + 8 * ((fbase + f) % Cfg::kStages); };
+          auto full_par = [&](uint32_t f) { return ((fbase + f) / Cfg::kStages) & 1u; };
+          auto wait_full = [&](uint32_t f) {
+            alive &= mbar_wait_lim(full_bar(f), full_par(f), abort_flag, p.status, 31, wait_lim);
           };
-          auto peek_full = [&](int f) -> bool {
-            return mbar_try_wait(bar_full + 8 * ((fbase + f) % Cfg::kStages), ((fbase + f) / Cfg::kStages) & 1) != 0;
-          };
-          auto release = [&](int f) { tc_commit(bar_empty + 8 * ((fbase + f) % Cfg::kStages)); };
-          // The tensor pipe accepts a tcgen05.mma only about as fast as it executes them, so this
-          // thread is busy for the whole execution time of a batch and every cycle it then spends
-          // finding out whether the next batch may start is a cycle the pipe idles. Polls for the
-          // NEXT batch are therefore started in the middle of the current one (`peek`, non-blocking)
-          // and only fall back to a blocking wait when they failed.
+          auto release = [&](uint32_t f) { tc_commit(bar_empty + 8 * ((fbase + f) % Cfg::kStages)); };
           // The tile index is a compile-time constant (std::integral_constant argument) so that the
           // per-tile state arrays are indexed statically and stay in registers.
-          auto issue_s = [&](auto gc, int e, auto&& peek) {   // S_g = Q_g * K(e)^T
+          auto issue_s = [&](auto gc, uint32_t e, auto&& peek) {   // S_g = Q_g * K(e)^T
             constexpr int g = decltype(gc)::value;
             if (!q_ready[g]) {
               alive &= mbar_wait_lim(bar_q + 8 * g, n_q[g] & 1, abort_flag, p.status, 32, wait_lim);
@@ -575,39 +519,40 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               q_ready[g] = true;
               ++n_q[g];
             }
-            const uint64_t kd = k_desc0 + slot_of(2 * e) * kSlotStep;
-            const uint64_t qd = q_desc[g];
+            const uint32_t kd = k_lo0 + ((fbase + 2 * e) % Cfg::kStages) * kSlotStep;
+            const uint32_t qd = q_lo[g];
             const uint32_t d_tmem = tS[g];
+            // 16 head-dim columns per step: 32 bytes inside a 64-column chunk, chunks kChunkBytes apart
+            umma_ss_lo<false>(d_tmem, qd, kd, desc_hi, idesc_qk);
 #pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-              // 16 head-dim columns per step: 32 bytes inside a 64-column chunk, chunks kChunkBytes apart
+            for (int ks = 1; ks < D / 16; ++ks) {
               const uint32_t off = (ks / 4) * kChunkStep + (ks % 4) * 2;
-              umma_ss(d_tmem, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+              umma_ss_lo<true>(d_tmem, qd + off, kd + off, desc_hi, idesc_qk);
               if (ks == D / 16 - 4) peek();
             }
             tc_commit(bar_s + 8 * g);
           };
-          auto issue_pv = [&](auto gc, int e, bool p_ready) {  // O_g += P_g * V(e)
+          auto issue_pv = [&](auto gc, uint32_t e, bool p_ready) {  // O_g += P_g * V(e)
             constexpr int g = decltype(gc)::value;
             // 16 keys per step = 16 rows of 128 bytes = 2048 bytes; P advances 8 TMEM columns
-            const uint64_t vd = v_desc0 + slot_of(2 * e + 1) * kSlotStep;
+            const uint32_t vd = v_lo0 + ((fbase + 2 * e + 1) % Cfg::kStages) * kSlotStep;
             const uint32_t a_tmem = tS[g];
             const uint32_t d_tmem = tO[g];
-            const uint32_t first = n_pv[g] > 0 ? 1u : 0u;
             if (n_pv[g] == 0 && n_units[g] > 0) {
-              // first write to O_g in this unit: the output group must have read out the previous one
+              // first write to O_g in this unit: whoever writes the output must have read out the previous one
               alive &= mbar_wait_lim(bar_ofree + 8 * g, (n_units[g] - 1) & 1, abort_flag, p.status, 33, wait_lim);
             }
             if (!p_ready) alive &= mbar_wait_lim(bar_p + 8 * g, n_p[g] & 1, abort_flag, p.status, 34 + g, wait_lim);
             tc_fence_after();
+            umma_ts_lo(d_tmem, a_tmem, vd, desc_hi, idesc_pv, n_pv[g] > 0 ? 1u : 0u);
 #pragma unroll
-            for (int ks = 0; ks < kBlock / 16; ++ks) {
-              umma_ts(d_tmem, a_tmem + 8 * ks, vd + ks * 128, idesc_pv, ks > 0 ? 1u : first);
+            for (int ks = 1; ks < kBlock / 16; ++ks) {
+              umma_ts_lo_acc(d_tmem, a_tmem + 8 * ks, vd + ks * 128, desc_hi, idesc_pv);
             }
             ++n_pv[g];
             ++n_p[g];
-            // last P*V of this tile in the unit: the output group may read O as soon as these MMAs
-            // retire, without waiting for the other tile
+            // last P*V of this tile in the unit: O may be read as soon as these MMAs retire, without
+            // waiting for the other tile
             if (n_pv[g] == cnt_g[g]) {
               tc_commit(bar_done + 8 * g);
               ++n_units[g];
@@ -619,25 +564,24 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
           if (n_sched > 0) {
             issued_any = true;
+            uint32_t cur = lds_u16(sched);
             {  // prologue: scores of the first visited block
-              const int kvb = T.sched[0];
               wait_full(0);
               tc_fence_after();
-              if (tile_visits<B64>(tabA, kvb)) issue_s(tile_a, 0, no_peek);
-              if (tile_visits<B64>(tabB, kvb)) issue_s(tile_b, 0, no_peek);
+              if (cur & kSchedA) issue_s(tile_a, 0, no_peek);
+              if (cur & kSchedB) issue_s(tile_b, 0, no_peek);
               release(0);
               if (n_sched == 1) tc_commit(bar_qfree);
             }
             bool ring_ok = false;   // V(e) and K(e+1) already seen complete
             bool pa_ok = false;     // P_A(e) already seen complete
-            for (int e = 0; e < n_sched; ++e) {
+            const uint32_t n = static_cast<uint32_t>(n_sched);
+            for (uint32_t e = 0; e < n; ++e) {
               if (!alive) break;
-              const int kvb = T.sched[e];
-              const bool has_next = e + 1 < n_sched;
-              const int kvb_next = has_next ? T.sched[e + 1] : 0;
-              const bool use_a = tile_visits<B64>(tabA, kvb), use_b = tile_visits<B64>(tabB, kvb);
-              const bool next_a = has_next && tile_visits<B64>(tabA, kvb_next);
-              const bool next_b = has_next && tile_visits<B64>(tabB, kvb_next);
+              const bool has_next = e + 1 < n;
+              const uint32_t nxt = has_next ? lds_u16(sched + 2 * (e + 1)) : 0u;
+              const bool use_a = (cur & kSchedA) != 0, use_b = (cur & kSchedB) != 0;
+              const bool next_a = (nxt & kSchedA) != 0, next_b = (nxt & kSchedB) != 0;
               if (!ring_ok) {
                 wait_full(2 * e + 1);                 // V(e)
                 if (has_next) wait_full(2 * e + 2);   // K(e+1)
@@ -646,26 +590,27 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               bool pb_ok = false;
               if (use_a) issue_pv(tile_a, e, pa_ok);
               if (next_a) {
-                issue_s(tile_a, e + 1, [&] { if (use_b) pb_ok = mbar_try_wait(bar_p + 8, n_p[1] & 1) != 0; });
+                issue_s(tile_a, e + 1, [&] { if (use_b) pb_ok = mbar_test_wait(bar_p + 8, n_p[1] & 1) != 0; });
               }
               if (use_b) issue_pv(tile_b, e, pb_ok);
               ring_ok = false;
               pa_ok = false;
               if (next_b) {
                 issue_s(tile_b, e + 1, [&] {
-                  bool ok = peek_full(2 * e + 3);                       // V(e+1)
-                  if (e + 2 < n_sched) ok = peek_full(2 * e + 4) && ok; // K(e+2)
+                  bool ok = mbar_test_wait(full_bar(2 * e + 3), full_par(2 * e + 3)) != 0;                  // V(e+1)
+                  if (e + 2 < n) ok = (mbar_test_wait(full_bar(2 * e + 4), full_par(2 * e + 4)) != 0) && ok; // K(e+2)
                   ring_ok = ok;
-                  if (next_a) pa_ok = mbar_try_wait(bar_p, n_p[0] & 1) != 0;
+                  if (next_a) pa_ok = mbar_test_wait(bar_p, n_p[0] & 1) != 0;
                 });
               }
-              if (e + 2 == n_sched) tc_commit(bar_qfree);   // the last S of the unit has been issued
+              if (e + 2 == n) tc_commit(bar_qfree);   // the last S of the unit has been issued
               release(2 * e + 1);
               if (has_next) release(2 * e + 2);
+              cur = nxt;
             }
           }
           if (!alive) break;
-          fbase += 2 * n_sched;
+          fbase += 2 * static_cast<uint32_t>(n_sched);
           mbar_arrive(bar_tempty + 8 * (k & 1));
         }
         // Keep this thread (and with it the CTA's shared memory and TMEM) alive until every MMA it
@@ -722,13 +667,16 @@ omni_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const int kvb = base + lane;
           bool a = false, b = false;
           if (kvb < p.nq) {
-            a = tile_visits<B64>(T.tab[0], kvb);
-            b = tile_visits<B64>(T.tab[1], kvb);
+            a = tile_visits<B64>(smem_u32(T.tab[0]), kvb);
+            b = tile_visits<B64>(smem_u32(T.tab[1]), kvb);
           }
           const uint32_t any = __ballot_sync(0xFFFFFFFFu, a || b);
           ca += __popc(__ballot_sync(0xFFFFFFFFu, a));
           cb += __popc(__ballot_sync(0xFFFFFFFFu, b));
-          if (a || b) T.sched[n + __popc(any & ((1u << lane) - 1u))] = static_cast<uint16_t>(kvb);
+          if (a || b) {
+            T.sched[n + __popc(any & ((1u << lane) - 1u))] =
+                static_cast<uint16_t>(kvb | (a ? kSchedA : 0) | (b ? kSchedB : 0));
+          }
           n += __popc(any);
         }
         if (lane == 0) {
@@ -786,7 +734,7 @@ static cudaError_t launch_ws_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, c
     cudaFuncAttributes fa;
     pd.err = cudaFuncGetAttributes(&fa, kern);
     if (pd.err != cudaSuccess) return;
-    if (2 * WsRegs<D>::kSoftmax + WsRegs<D>::kRole + WsRegs<D>::kOutput > 4 * fa.numRegs) {
+    if (2 * kSoftmaxRegs + kOtherRegs > 3 * fa.numRegs) {
       pd.err = cudaErrorLaunchOutOfResources;
       return;
     }

@@ -57,16 +57,54 @@ def shard_qkv(t: Tensor, rank: int, world: int) -> Tensor:
     return t.reshape(B * H, N, D)[lo:hi].unsqueeze(0)
 
 
-def all_gather_outputs(local_out: Tensor, total_bh: int, group=None) -> Tensor:
+class ShardingError(RuntimeError):
+    """A peer rank reported a failure, or did not show up for a host-side hand-shake or the gather in time."""
+
+
+def agree_to_launch(ok: bool, group=None, timeout_s: float = 30.0) -> None:
+    """Host-side hand-shake before a sharded step: every rank says whether it is ready to launch
+    (``ok=False`` from a rank whose own preparation raised). Returns when all ranks are; raises
+    ShardingError on every rank when any rank is not, or when a rank does not answer within
+    ``timeout_s``, so that no rank launches work whose result nobody will collect. Runs on CPU tensors
+    (use a gloo group next to the NCCL one on GPUs): the ranks learn of a failure on the host, with
+    none of their kernels or collectives in flight. The reference is single-GPU and has no
+    counterpart; its whole error story is a cudaGetLastError after the launch
+    (omni-attn-mma/mma/omni_attn_shared_kv.cu:1005-1008)."""
+    import datetime
+
+    import torch.distributed as dist
+
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32)
+    try:
+        work = dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group, async_op=True)
+        work.wait(timeout=datetime.timedelta(seconds=timeout_s))
+    except Exception as e:  # a peer that never joins ends the wait with the backend's timeout error
+        raise ShardingError(f"a rank did not answer the launch hand-shake within {timeout_s} s: {e}") from e
+    if int(flag[0]) != 1:
+        raise ShardingError("a rank reported a failure before launch" if ok else "this rank failed before launch")
+
+
+def all_gather_outputs(local_out: Tensor, total_bh: int, group=None, timeout_s: Optional[float] = None) -> Tensor:
     """Optional epilogue: gather every rank's [1, n_local, N, D] output into [total_bh, N, D] on all
-    ranks (NCCL on GPUs, gloo on CPU). Not part of the timed forward."""
+    ranks (NCCL on GPUs, gloo on CPU). Not part of the timed forward. With ``timeout_s`` the host gives
+    up waiting after that many seconds and raises ShardingError (a rank that skipped the gather)."""
+    import datetime
+
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
     N, D = local_out.shape[2:]
     sizes = [shard_range(total_bh, r, world) for r in range(world)]
     parts = [torch.empty(hi - lo, N, D, dtype=local_out.dtype, device=local_out.device) for lo, hi in sizes]
-    dist.all_gather(parts, local_out.reshape(-1, N, D).contiguous(), group=group)
+    mine = local_out.reshape(-1, N, D).contiguous()
+    if timeout_s is None:
+        dist.all_gather(parts, mine, group=group)
+    else:
+        try:
+            work = dist.all_gather(parts, mine, group=group, async_op=True)
+            work.wait(timeout=datetime.timedelta(seconds=timeout_s))
+        except Exception as e:
+            raise ShardingError(f"all-gather of the outputs did not complete within {timeout_s} s: {e}") from e
     return torch.cat(parts, 0)
 
 

@@ -101,6 +101,34 @@ def main(ref_dir: str) -> None:
                                             device="cpu", output_file=os.path.join(tmp, "g.pt"), seed=24)
     finish("ref_fcp_n320_d128_blk64", d["Q_fp32"], d["K_fp32"], d["V_fp32"], d["omni_block_mask"], d["dense_mask"])
 
+    # 9. the Transfusion model's attention core with its tanh soft-cap (transfusion_pytorch/transfusion.py:
+    # 963-983), on case 4's inputs and dense mask, caps 50 (the model's default) and 4. The package cannot be
+    # imported here (einx and others are missing), so the two pure-torch helpers the core uses, softclamp
+    # (:298-299) and max_neg_value (:301-302), are taken out of its source file and executed; the remaining
+    # lines of the core are torch operators written out below as they stand there (einx.where with the
+    # pattern 'b i j, b h i j, -> b h i j' is torch.where with the mask broadcast over heads).
+    import ast
+
+    src = open(os.path.join(ref_dir, "..", "transfusion_pytorch", "transfusion.py")).read()
+    helpers = {"torch": torch}
+    for node in ast.parse(src).body:
+        if isinstance(node, ast.FunctionDef) and node.name in ("softclamp", "max_neg_value"):
+            exec(compile(ast.Module([node], []), "transfusion.py", "exec"), helpers)
+    z = np.load(os.path.join(out_dir, "ref_interleaved_n512_d64.npz"))
+    q, k, v = (torch.from_numpy(z[n]).float() for n in "qkv")
+    attn_mask = torch.from_numpy(np.unpackbits(z["dense_mask"], axis=-1)[..., :512].astype(bool))[:, 0]   # [b, i, j]
+    scale = 64 ** -0.5
+    res = {}
+    for cap in (50.0, 4.0):
+        sim = torch.einsum("bhid,bhjd->bhij", q * scale, k)
+        sim = helpers["softclamp"](sim, cap)
+        sim = torch.where(attn_mask[:, None], sim, torch.full_like(sim, helpers["max_neg_value"](sim)))
+        attn = sim.softmax(dim=-1)
+        res[f"out_cap{int(cap)}"] = torch.einsum("bhij,bhjd->bhid", attn, v).numpy()
+        res[f"lse_cap{int(cap)}"] = torch.logsumexp(sim, dim=-1).numpy()
+    np.savez(os.path.join(out_dir, "ref_softcap_interleaved_n512_d64.npz"), **res)
+    print("ref_softcap_interleaved_n512_d64 saved (inputs and mask: ref_interleaved_n512_d64)")
+
 
 if __name__ == "__main__":
     here = os.path.dirname(os.path.abspath(__file__))

@@ -263,3 +263,32 @@ print("threads ok")
 """ % (ROOT, os.path.join(ROOT, "tests"))
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "threads ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_next_call_is_right(cuda_device):
+    """Bounded waits: with a budget of one cycle (omni_attn_set_wait_cycles) every hand-over that is not
+    already there when a role asks for it counts as run out; the CTAs give up cleanly - status
+    OMNI_STATUS_WAIT_TIMEOUT with the place in the upper bits, the call returns, nothing is left in flight -
+    and an ordinary call right afterwards, on the same context, is correct."""
+    lib = ops.load_library()
+    g = load_golden("ref_fcp_n384_d128")
+    dev = cuda_device
+    q, k, v = (g[x].to(dev).contiguous() for x in "qkv")
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    lib.omni_attn_set_wait_cycles(1)
+    try:
+        ops.omni_attention_forward_out(q, k, v, out, g["bm"], q.shape[2], status=status, kernel="ws")
+        torch.cuda.synchronize()
+    finally:
+        lib.omni_attn_set_wait_cycles(0)       # back to the default budget
+    code = int(status.item())
+    assert code & 0xFF == ops.STATUS_WAIT_TIMEOUT and (code >> 8) > 0, hex(code)
+    with pytest.raises(ops.OmniAttnError, match="gave up waiting"):
+        lib.omni_attn_set_wait_cycles(1)
+        try:
+            omni_attention(q, k, v, g["bm"], check_status=True)
+        finally:
+            lib.omni_attn_set_wait_cycles(0)
+    good, lse = run(g["q"], g["k"], g["v"], g["bm"], dev)
+    assert_parity(good, lse, g["out"], g["lse"], "call after a timed-out one")

@@ -153,3 +153,96 @@ def test_blockwise_gradient_oracle_matches_the_autograd_oracle():
         dense = orc.to_dense_mask_slice(bm, 0, h)
         for qb in range(4):
             assert torch.equal(orc.mask_block_rows(bm, 0, h, qb), dense[qb * 128:(qb + 1) * 128])
+
+
+# ---- the Transfusion attention core with its tanh soft-cap ---------------------------------------------------
+TRANSFUSION_SRC = os.path.normpath(os.path.join(REF_DIR, "..", "transfusion_pytorch", "transfusion.py"))
+
+
+def _softcap_golden():
+    import numpy as np
+    from conftest import GOLDEN_DIR
+
+    z = np.load(os.path.join(GOLDEN_DIR, "ref_softcap_interleaved_n512_d64.npz"))
+    return {k: torch.from_numpy(z[k]) for k in z.files}
+
+
+def test_softclamp_is_the_references_function():
+    """oracle.softclamp against the reference's own two-line function (transfusion_pytorch/transfusion.py:
+    298-299), taken out of its source file (the package itself cannot be imported: einx is missing)."""
+    if not os.path.exists(TRANSFUSION_SRC):
+        pytest.skip("reference checkout not present")
+    import ast
+
+    ns = {"torch": torch}
+    for node in ast.parse(open(TRANSFUSION_SRC).read()).body:
+        if isinstance(node, ast.FunctionDef) and node.name == "softclamp":
+            exec(compile(ast.Module([node], []), TRANSFUSION_SRC, "exec"), ns)
+    t = torch.randn(4, 97, generator=torch.Generator().manual_seed(2)) * 30
+    for cap in (50.0, 4.0, 15.0):
+        assert torch.equal(orc.softclamp(t, cap), ns["softclamp"](t, cap))
+    assert torch.equal(orc.softclamp(t), ns["softclamp"](t))
+
+
+@pytest.mark.parametrize("cap", [50, 4])
+def test_softcap_branch_of_the_oracle_matches_the_reference_core(cap):
+    """attention_dense_mask(softcap=) against the golden written from the reference's own softclamp /
+    max_neg_value and the operators of its attention core (tests/golden/make_golden.py, case 9)."""
+    g = load_golden("ref_interleaved_n512_d64")
+    s = _softcap_golden()
+    out, lse = orc.attention_dense_mask(g["q"].float(), g["k"].float(), g["v"].float(), orc.to_score_mask(g["dense"]),
+                                        softcap=float(cap))
+    assert torch.allclose(out, s[f"out_cap{cap}"], atol=3e-6, rtol=1e-5)
+    assert torch.allclose(lse, s[f"lse_cap{cap}"], atol=3e-6, rtol=1e-5)
+
+
+def test_attention_forward_restatement_reproduces_the_core_golden():
+    """transfusion_attention_forward with pass-through projections is the bare core: it must give the
+    cap-50 golden."""
+    g = load_golden("ref_interleaved_n512_d64")
+    s = _softcap_golden()
+
+    class Bare:
+        scale, softcap_value, laser, laser_softclamp_value, to_gates = 64 ** -0.5, 50.0, False, 15.0, None
+        to_qk = staticmethod(lambda x: (g["q"].float(), g["k"].float()))
+        to_v = staticmethod(lambda x: g["v"].float())
+        to_out = staticmethod(lambda o: o)
+        dropout = staticmethod(lambda a: a)
+
+    out = orc.transfusion_attention_forward(Bare, None, attn_mask=g["dense"][:, 0])
+    assert torch.allclose(out, s["out_cap50"], atol=3e-6, rtol=1e-5)
+
+
+def test_modality_position_builder_matches_the_references_builder():
+    """create_omni_block_mask_from_modality_positions (this package, CPU path) against the reference's
+    builder of the same name (omni-attn-mma/omni_attn_torch.py:1518-1736) on spans aligned to the block
+    size, where the reference needs nothing from the transfusion package: equal dense expansions."""
+    if not os.path.exists(os.path.join(REF_DIR, "omni_attn_torch.py")):
+        pytest.skip("reference checkout not present")
+    sys.path.insert(0, REF_DIR)
+    try:
+        import omni_attn_torch as ref
+    finally:
+        sys.path.remove(REF_DIR)
+    from omni_attention_b200.block_mask import create_omni_block_mask_from_modality_positions
+
+    gen = torch.Generator().manual_seed(12)
+    for N in (512, 1024):
+        nb = N // 128
+        rows = []
+        for _ in range(2):                      # two batch elements, up to three aligned image spans each
+            spans, pos = [], 0
+            while pos < nb and len(spans) < 3:
+                pos += int(torch.randint(0, 3, (1,), generator=gen))
+                ln = int(torch.randint(1, 3, (1,), generator=gen))
+                if pos + ln > nb:
+                    break
+                spans.append([1, pos * 128, ln * 128])
+                pos += ln
+            rows.append(spans + [[0, 0, 0]] * (3 - len(spans)))
+        mp = torch.tensor(rows, dtype=torch.int32)
+        theirs = ref.create_omni_block_mask_from_modality_positions(mp, 2, 2, N, N, 128, 128, device="cpu")
+        assert theirs.partial_block_masks is None          # aligned spans: the reference built no PARTIAL block
+        mine = create_omni_block_mask_from_modality_positions(mp, 2, 2, N, N, 128, 128, device="cpu")
+        assert torch.equal(mine.to_dense_mask(), theirs.to_dense_mask())
+        assert torch.equal(orc.to_dense_mask_loops(mine), orc.naive_attn_mask(N, mp)[:, None].expand(-1, 2, -1, -1))

@@ -74,3 +74,71 @@ def test_two_rank_gloo_shard_and_gather():
     port = _free_port()
     mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
     assert dict(ret) == {0: 1, 1: 1}
+
+
+def _failing_worker(rank, world, port, ret, scenario):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    launched = False
+    try:
+        if scenario == "raise_before_launch":
+            # rank 1's preparation raises; it still answers the hand-shake, with ok=False, and every
+            # rank learns of it on the host before anything is launched
+            ok = True
+            try:
+                if rank == 1:
+                    raise ValueError("mask construction failed on this rank")
+            except ValueError:
+                ok = False
+            try:
+                sharding.agree_to_launch(ok, timeout_s=20.0)
+                launched = True
+            except sharding.ShardingError as e:
+                ret[rank] = ("refused", str(e))
+        elif scenario == "absent_from_handshake":
+            # rank 1 never joins: rank 0's hand-shake gives up after its host timeout
+            if rank == 0:
+                try:
+                    sharding.agree_to_launch(True, timeout_s=2.0)
+                    launched = True
+                except sharding.ShardingError as e:
+                    ret[rank] = ("refused", str(e))
+            else:
+                ret[rank] = ("absent", "")
+        elif scenario == "skips_the_gather":
+            # both ranks run their (stand-in) forward; rank 1 then skips the optional gather
+            sharding.agree_to_launch(True, timeout_s=20.0)
+            local = torch.full((1, 1, 128, 64), float(rank))
+            if rank == 0:
+                try:
+                    sharding.all_gather_outputs(local, world, timeout_s=2.0)
+                    ret[rank] = ("gathered", "")
+                except sharding.ShardingError as e:
+                    ret[rank] = ("gave_up", str(e))
+            else:
+                ret[rank] = ("skipped", "")
+        assert not launched or scenario == "skips_the_gather"
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+@pytest.mark.parametrize("scenario,expect", [
+    ("raise_before_launch", {0: "refused", 1: "refused"}),
+    ("absent_from_handshake", {0: "refused", 1: "absent"}),
+    ("skips_the_gather", {0: "gave_up", 1: "skipped"}),
+])
+def test_host_side_failures_between_ranks(scenario, expect):
+    """A rank that fails before launch, one that never shows up, and one that skips the optional
+    gather: the others find out on the host (a hand-shake on CPU tensors, a gather with a host
+    timeout), raise ShardingError and launch nothing. No GPU is involved."""
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_failing_worker, args=(world, _free_port(), ret, scenario), nprocs=world, join=True)
+    assert {k: v[0] for k, v in dict(ret).items()} == expect
+    if scenario == "raise_before_launch":
+        assert "reported a failure" in ret[0][1] and "this rank failed" in ret[1][1]
