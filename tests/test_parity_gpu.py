@@ -497,3 +497,25 @@ def test_running_maximum_that_keeps_moving(cuda_device, kernel, D, dtype):
     out, lse = run(q, k, v, bm, cuda_device, kernel)
     ref_out, ref_lse = orc.block_mask_attention(q, k, v, bm)
     assert_parity(out, lse, ref_out, ref_lse, f"moving maximum D={D}")
+
+
+@pytest.mark.parametrize("seed", [0, 1, 7])
+def test_config_c4_on_the_inputs_the_bench_times(cuda_device, seed):
+    """The bench's rank `seed` draws its mask with seed = rank and its Q, K, V on the device with seed
+    1234 + rank (bench.device_qkv): the same inputs here, sampled rows of every head against the scalar
+    oracle, and the fast kernel against the plain one everywhere."""
+    import bench
+
+    cfg = inputs.CONFIGS["C4"]
+    bm, _ = inputs.make_block_mask(cfg, seed=seed, B=1)
+    q, k, v = bench.device_qkv(1, cfg.H, cfg.N, cfg.D, cfg.dtype, 1234 + seed, cuda_device, cfg.qkv_scale)
+    out, lse = omni_attention(q, k, v, bm, return_lse=True, check_status=True)
+    out_s, lse_s = omni_attention(q, k, v, bm, return_lse=True, check_status=True, kernel="simple")
+    g = torch.Generator().manual_seed(100 + seed)
+    rb, rq = _sample_rows(1, cfg.H, cfg.N, 192, g)
+    rq[:6] = [0, 127, 128, cfg.N - 1, cfg.N - 128, 4097]
+    so, sl = scalar.oracle_rows(q.cpu(), k.cpu(), v.cpu(), bm, rb, rq)
+    got = out.float().cpu().view(cfg.H, cfg.N, cfg.D)[rb, rq]
+    got_l = lse.cpu().view(cfg.H, cfg.N)[rb, rq]
+    assert_parity(got, got_l, so, sl, f"C4 bench inputs, seed {seed}")
+    assert_parity(out, lse, out_s.float(), lse_s, f"C4 bench inputs, seed {seed}: ws vs simple")
