@@ -117,14 +117,21 @@ __device__ __forceinline__ void bwd_load_tile(uint32_t dst, const CUtensorMap* t
   for (int c = 0; c < BwdCfg<D>::kChunks; ++c) tma_load_2d(dst + c * BwdCfg<D>::kChunkBytes, tm, bar, c * 64, y);
 }
 
+// Every tcgen05.mma occupies the issuing thread for about as long as the tensor pipe needs for it, so
+// whatever else that thread executes per MMA is time with nothing queued: the descriptors are advanced
+// as 32-bit low words (the high word is one constant) and the accumulate flags are compile-time
+// constants wherever they can be.
+constexpr uint32_t kBwdDescHi = umma_desc_hi_sw128(1024);
+
 // acc[128 x 128] = A[128 x D] * B[128 x D]^T, both tiles row-major with D contiguous (K-major).
 template <int D>
 __device__ __forceinline__ void bwd_mma_ss(uint32_t d_tmem, uint32_t sA, uint32_t sB, uint32_t idesc) {
+  const uint32_t a_lo = umma_desc_lo(sA, 16), b_lo = umma_desc_lo(sB, 16);
+  umma_ss_lo<false>(d_tmem, a_lo, b_lo, kBwdDescHi, idesc);
 #pragma unroll
-  for (int k = 0; k < D / 16; ++k) {
-    const uint32_t off = (k / 4) * BwdCfg<D>::kChunkBytes + (k % 4) * 32;
-    umma_ss(d_tmem, umma_smem_desc_sw128(sA + off, 16, 1024), umma_smem_desc_sw128(sB + off, 16, 1024), idesc,
-            k > 0 ? 1u : 0u);
+  for (int k = 1; k < D / 16; ++k) {
+    const uint32_t off = ((k / 4) * BwdCfg<D>::kChunkBytes + (k % 4) * 32) >> 4;
+    umma_ss_lo<true>(d_tmem, a_lo + off, b_lo + off, kBwdDescHi, idesc);
   }
 }
 
@@ -133,10 +140,11 @@ __device__ __forceinline__ void bwd_mma_ss(uint32_t d_tmem, uint32_t sA, uint32_
 template <int D>
 __device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t sB, uint32_t idesc,
                                            bool accumulate) {
+  const uint32_t b_lo = umma_desc_lo(sB, BwdCfg<D>::kChunkBytes);
+  umma_ts_lo(d_tmem, a_tmem, b_lo, kBwdDescHi, idesc, accumulate ? 1u : 0u);
 #pragma unroll
-  for (int k = 0; k < kBlock / 16; ++k) {
-    umma_ts(d_tmem, a_tmem + 8 * k, umma_smem_desc_sw128(sB + k * 2048, BwdCfg<D>::kChunkBytes, 1024), idesc,
-            (accumulate || k > 0) ? 1u : 0u);
+  for (int k = 1; k < kBlock / 16; ++k) {
+    umma_ts_lo_acc(d_tmem, a_tmem + 8 * k, b_lo + k * 128, kBwdDescHi, idesc);
   }
 }
 
@@ -146,10 +154,11 @@ __device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uin
 template <int D>
 __device__ __forceinline__ void bwd_mma_ts_split(uint32_t d_tmem, uint32_t a_region, uint32_t a_off, uint32_t sB,
                                                  uint32_t idesc, bool accumulate) {
+  const uint32_t b_lo = umma_desc_lo(sB, BwdCfg<D>::kChunkBytes);
+  umma_ts_lo(d_tmem, a_region + a_off, b_lo, kBwdDescHi, idesc, accumulate ? 1u : 0u);
 #pragma unroll
-  for (int k = 0; k < kBlock / 16; ++k) {
-    umma_ts(d_tmem, a_region + 64 * (k / 4) + a_off + 8 * (k % 4),
-            umma_smem_desc_sw128(sB + k * 2048, BwdCfg<D>::kChunkBytes, 1024), idesc, (accumulate || k > 0) ? 1u : 0u);
+  for (int k = 1; k < kBlock / 16; ++k) {
+    umma_ts_lo_acc(d_tmem, a_region + 64 * (k / 4) + a_off + 8 * (k % 4), b_lo + k * 128, kBwdDescHi, idesc);
   }
 }
 
