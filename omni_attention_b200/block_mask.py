@@ -51,9 +51,16 @@ class OmniBlockMask:
     Q_BLOCK_SIZE: int = 128
     KV_BLOCK_SIZE: int = 128
     partial_block_mask_indices: Optional[Tensor] = None
-    partial_block_masks: Optional[Tensor] = None
+    partial_block_masks: Optional[Tensor] = None   # a property, see below: may be expanded on first read
     # Device-side copies and the bit-packed partial pool, filled lazily by the operator.
     _cache: dict = field(default_factory=dict, repr=False, compare=False)
+
+    def set_lazy_partial_pool(self, make) -> None:
+        """``make()`` returns the bool pool; it is called the first time ``partial_block_masks`` is read.
+        Used by builders that hold the pool in another form (bit-packed on the GPU) and whose consumers
+        never need the byte-per-element copy."""
+        self.__dict__["_pool"] = None
+        self.__dict__["_pool_make"] = make
 
     @property
     def num_q_blocks(self) -> int:
@@ -87,10 +94,13 @@ class OmniBlockMask:
         """
         B, H, nq = self.kv_num_blocks.shape
         fl = lambda t: None if t is None else t.reshape(B * H, *t.shape[2:])[start:stop].unsqueeze(0)
-        return OmniBlockMask(
+        out = OmniBlockMask(
             fl(self.kv_num_blocks), fl(self.kv_indices), fl(self.block_mask_types), self.q_len,
-            self.kv_len, self.Q_BLOCK_SIZE, self.KV_BLOCK_SIZE, fl(self.partial_block_mask_indices),
-            self.partial_block_masks)
+            self.kv_len, self.Q_BLOCK_SIZE, self.KV_BLOCK_SIZE, fl(self.partial_block_mask_indices), None)
+        # the pool is shared as it is: expanded, or still to be expanded on first read
+        out.__dict__["_pool"] = self.__dict__.get("_pool")
+        out.__dict__["_pool_make"] = (lambda: self.partial_block_masks) if self.__dict__.get("_pool_make") else None
+        return out
 
     def visited_blocks(self) -> int:
         """Listed entries that are actually computed (type FULL, CAUSAL or PARTIAL)."""
@@ -109,6 +119,26 @@ class OmniBlockMask:
     def to_dense_mask(self) -> Tensor:
         """Boolean [B, H, q_len, kv_len], True = attend."""
         return dense_mask_from_blocks(self)
+
+
+def _get_partial_pool(self):
+    pool = self.__dict__.get("_pool")
+    make = self.__dict__.get("_pool_make")
+    if pool is None and make is not None:
+        pool = make()
+        self.__dict__["_pool"] = pool
+        self.__dict__["_pool_make"] = None
+    return pool
+
+
+def _set_partial_pool(self, value):
+    self.__dict__["_pool"] = value
+    self.__dict__["_pool_make"] = None
+
+
+# The dataclass keeps the reference's field name and position; reads and writes go through a
+# property so that a builder may leave the byte-per-element pool unexpanded until someone asks.
+OmniBlockMask.partial_block_masks = property(_get_partial_pool, _set_partial_pool)
 
 
 def dense_mask_from_blocks(bm: OmniBlockMask, bh_range: Optional[Tuple[int, int]] = None) -> Tensor:
@@ -365,6 +395,24 @@ def _limits_from_modality_tensor(modality_positions: Tensor, seq_len: int, padde
     limits = torch.where(pad, torch.full_like(limits, -1), limits)
     plain &= ~pad
     return limits, plain
+
+
+def count_partial_tiles(limits: Tensor, plain: Tensor, block: int = 128) -> int:
+    """Number of PARTIAL tiles of the row-limit mask ``limits`` [B, N] (the same typing rule as
+    ``block_mask_from_row_limits`` and the GPU builder, evaluated from the smallest and largest limit
+    of every block of rows; the pool is shared by the heads)."""
+    B, N = limits.shape
+    nq = N // block
+    lim = limits.long().view(B, nq, block)
+    lim_min, lim_max = lim.min(-1).values, lim.max(-1).values
+    q = torch.arange(N, device=limits.device).view(1, nq, block)
+    causal_block = (plain.view(B, nq, block) & (lim == q)).all(-1)
+    lo = torch.div(lim_min + 1, block, rounding_mode="floor")   # first KV block that is not FULL
+    hi = torch.div(lim_max, block, rounding_mode="floor")       # last KV block that is listed
+    cnt = (hi - lo + 1).clamp(min=0)
+    qb = torch.arange(nq, device=limits.device).view(1, nq)
+    cnt = cnt - ((lo <= qb) & (qb <= hi) & causal_block).long()  # a CAUSAL diagonal tile is not PARTIAL
+    return int(cnt.sum().item())
 
 
 def create_omni_block_mask_from_modality_positions(modality_positions: Tensor, batch: int, nheads: int, q_len: int,

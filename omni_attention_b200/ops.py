@@ -135,10 +135,16 @@ def pack_partial_masks(partial_block_masks: Tensor) -> Tensor:
 def build_block_mask_cuda(modality_positions: Tensor, batch: int, nheads: int, seq_len: int, padded: int,
                           device: torch.device) -> OmniBlockMask:
     """Runs omni_attn_build_mask_sm100 on ``device`` and wraps its outputs in an OmniBlockMask whose
-    tensors stay on the device. The PARTIAL pool is sized from the number of spans (every span start
-    or end can make at most one Q block row and one KV block column of tiles partial) and the call is
-    repeated once with the exact size if that guess was too small."""
+    tensors stay on the device. Nothing here waits for the GPU when ``modality_positions`` is a host
+    tensor: the number of PARTIAL tiles, which sizes the pool, is counted on the host from the span
+    table (O(B*N*M) integer arithmetic). The kernels write the pool bit-packed, which is what the
+    attention kernels read; the container's byte-per-element ``partial_block_masks`` is expanded from it
+    only if somebody reads that field."""
+    from .block_mask import _limits_from_modality_tensor, count_partial_tiles
+
     lib = load_library()
+    limits, plain = _limits_from_modality_tensor(modality_positions, int(seq_len), int(padded))
+    need = count_partial_tiles(limits, plain)
     mp = modality_positions.to(device=device, dtype=torch.int32).contiguous()
     M = int(mp.shape[1])
     nq = padded // 128
@@ -148,31 +154,36 @@ def build_block_mask_cuda(modality_positions: Tensor, batch: int, nheads: int, s
     pidx = torch.empty_like(idx)
     count = torch.zeros(1, dtype=torch.int32, device=device)
     scratch = torch.empty(2 * batch * nq, dtype=torch.int32, device=device)
-    capacity = max(16, batch * (2 * M + 2) * 4)
+    bits = torch.empty(max(need, 1), 128, 4, dtype=torch.int32, device=device)
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream().cuda_stream
-        while True:
-            bits = torch.empty(capacity, 128, 4, dtype=torch.int32, device=device)
-            _check(lib.omni_attn_build_mask_sm100(_ptr(mp), batch, M, nheads, int(seq_len), int(padded), nb.data_ptr(),
-                                                  idx.data_ptr(), typ.data_ptr(), pidx.data_ptr(), bits.data_ptr(), None,
-                                                  capacity, count.data_ptr(), scratch.data_ptr(), scratch.numel() * 4,
-                                                  stream))
-            need = int(count.item())
-            if need <= capacity:
-                break
-            capacity = need
-    bits = bits[:need].contiguous()
-    # the container's pool field is the reference's bool [P,128,128]; expand the bit tiles once
-    w = bits.to(torch.int64) & 0xFFFFFFFF
-    pool = ((w.unsqueeze(-1) >> torch.arange(32, device=device)) & 1).bool().view(need, 128, 128)
-    bm = OmniBlockMask(nb, idx, typ, padded, padded, 128, 128, pidx, pool)
-    ready = torch.cuda.Event()
-    ready.record(torch.cuda.current_stream(device))
-    for pack in (True, False):
-        bm._cache[(str(device), pack)] = {"nb": nb, "idx": idx, "typ": typ, "pidx": pidx,
-                                          "pbool": None if pack or need == 0 else pool,
-                                          "pbits": bits if pack and need > 0 else None, "num_partial": need,
-                                          "ready": ready, "stream": torch.cuda.current_stream(device).cuda_stream}
+        _check(lib.omni_attn_build_mask_sm100(_ptr(mp), batch, M, nheads, int(seq_len), int(padded), nb.data_ptr(),
+                                              idx.data_ptr(), typ.data_ptr(), pidx.data_ptr(), bits.data_ptr(), None,
+                                              need, count.data_ptr(), scratch.data_ptr(), scratch.numel() * 4,
+                                              stream))
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(device))
+        built_on = torch.cuda.current_stream(device).cuda_stream
+    bits = bits[:need]
+    bm = OmniBlockMask(nb, idx, typ, padded, padded, 128, 128, pidx, None)
+
+    def expand_pool() -> Tensor:
+        # first read of the reference-shaped pool: also the place where the host count is checked
+        # against the one the kernels made (reading it waits for the GPU, which this read does anyway)
+        cur = torch.cuda.current_stream(device)
+        if cur.cuda_stream != built_on:
+            cur.wait_event(ready)
+        if int(count.item()) != need:
+            raise RuntimeError(f"mask builder: the kernels counted {int(count.item())} PARTIAL tiles, the host {need}")
+        shifts = torch.arange(32, dtype=torch.int32, device=device)
+        return ((bits.unsqueeze(-1) >> shifts) & 1).bool().view(need, 128, 128)
+
+    bm.set_lazy_partial_pool(expand_pool)
+    # what the attention calls use; a caller that asks for the byte-per-element pool (pack_bits=False)
+    # gets it through the container's field, expanded then
+    bm._cache[(str(device), True)] = {"nb": nb, "idx": idx, "typ": typ, "pidx": pidx, "pbool": None,
+                                      "pbits": bits if need > 0 else None, "num_partial": need,
+                                      "ready": ready, "stream": built_on}
     return bm
 
 

@@ -211,3 +211,44 @@ def test_retile_64_blocks_to_128_keeps_the_pattern():
     assert r.q_len == 384
     assert torch.equal(dense_mask_from_blocks(r)[:, :, :320, :320], d300)
     assert not bool(dense_mask_from_blocks(r)[:, :, 320:].any())
+
+
+def test_partial_tile_count_from_row_limits_is_the_pool_size():
+    """The host-side count that sizes the GPU builder's pool is the number of pool entries the CPU
+    builder makes, for span tables with unaligned, overlapping, empty and out-of-range spans and
+    lengths with and without padding."""
+    from omni_attention_b200.block_mask import _limits_from_modality_tensor, count_partial_tiles
+
+    g = torch.Generator().manual_seed(5)
+    for trial in range(40):
+        B = int(torch.randint(1, 4, (1,), generator=g))
+        M = int(torch.randint(0, 6, (1,), generator=g))
+        seq_len = int(torch.randint(1, 1500, (1,), generator=g))
+        pad = -(-seq_len // 128) * 128
+        mp = torch.zeros(B, M, 3, dtype=torch.long)
+        if M:
+            mp[:, :, 1] = torch.randint(0, seq_len + 200, (B, M), generator=g)
+            mp[:, :, 2] = torch.randint(0, 700, (B, M), generator=g)
+        limits, plain = _limits_from_modality_tensor(mp, seq_len, pad)
+        bm = block_mask_from_row_limits(limits, 2, plain, 128, True)
+        assert count_partial_tiles(limits, plain) == bm.partial_block_masks.shape[0], (trial, seq_len, mp.tolist())
+
+
+def test_partial_pool_can_be_left_unexpanded_until_it_is_read():
+    bm = create_causal_omni_block_mask(1, 2, 256, 256)
+    calls = []
+
+    def make():
+        calls.append(1)
+        return torch.ones(3, 128, 128, dtype=torch.bool)
+
+    bm.set_lazy_partial_pool(make)
+    part = bm.slice_heads(0, 1)            # shares the pool without expanding it
+    assert calls == []
+    assert part.partial_block_masks.shape == (3, 128, 128) and calls == [1]
+    assert bm.partial_block_masks is part.partial_block_masks and calls == [1]
+    bm.partial_block_masks = None          # plain assignment still works
+    assert bm.partial_block_masks is None
+    fresh = OmniBlockMask(bm.kv_num_blocks, bm.kv_indices, bm.block_mask_types, 256, 256, 128, 128, None,
+                          torch.zeros(1, 128, 128, dtype=torch.bool))
+    assert fresh.partial_block_masks.shape == (1, 128, 128)
