@@ -475,16 +475,125 @@ def _stack_block_masks(parts, B: int, H: int) -> OmniBlockMask:
     return bm
 
 
+def _retile_by_quadrants(bm: OmniBlockMask, block: int) -> OmniBlockMask:
+    """``retile_block_mask`` for a source block size that divides ``block``: every target tile is r x r
+    source blocks (r = block / source size), so its type and, where it is PARTIAL, its element mask
+    follow from those r*r list entries alone. Nothing of size N x N is built; the work is one small
+    grid per (batch, head) plus one [block, block] tile per PARTIAL target tile. Same expansion rules
+    as ``dense_mask_from_blocks``; heads of a batch element whose lists equal head 0's share its
+    pool entries."""
+    src = bm.Q_BLOCK_SIZE
+    r = block // src
+    B, H, nqs, mb = bm.kv_indices.shape
+    nks = bm.num_kv_blocks
+    dev = bm.device
+    BH = B * H
+    n_pad = -(-max(bm.q_len, bm.kv_len) // block) * block
+    nq = n_pad // block
+    G = nq * r                                   # source blocks per side after padding
+    flat = lambda t: t.reshape(BH, *t.shape[2:])
+    nb = flat(bm.kv_num_blocks).long().clamp(0, mb)
+    idx = flat(bm.kv_indices).long()
+    typ = flat(bm.block_mask_types).long()
+    listed = (torch.arange(mb, device=dev) < nb.unsqueeze(-1)) & (idx >= 0) & (idx < nks)
+    have_pool = bm.partial_block_mask_indices is not None and bm.partial_block_masks is not None
+    if have_pool:
+        pidx = flat(bm.partial_block_mask_indices).long()
+        usable = (pidx >= 0) & (pidx < bm.partial_block_masks.shape[0])
+    else:
+        pidx = torch.full_like(idx, -1)
+        usable = torch.zeros_like(listed)
+    is_partial = listed & (typ == BlockMaskType.PARTIAL) & usable
+    is_causal = listed & ((typ == BlockMaskType.CAUSAL) | ((typ == BlockMaskType.PARTIAL) & ~usable))
+    is_full = listed & (typ == BlockMaskType.FULL)
+
+    # state of every source block: bit 0 = FULL listed, bit 1 = CAUSAL listed, pool index of a PARTIAL entry
+    def scatter(sel: Tensor, value: Tensor, into: Tensor) -> None:
+        i0, i1, i2 = sel.nonzero(as_tuple=True)
+        into[i0, i1, idx[i0, i1, i2]] = value[i0, i1, i2] if value.dim() else value
+
+    one = torch.ones((), dtype=torch.bool, device=dev)
+    g_full = torch.zeros(BH, G, G, dtype=torch.bool, device=dev)
+    g_causal = torch.zeros_like(g_full)
+    g_pool = torch.full((BH, G, G), -1, dtype=torch.long, device=dev)
+    scatter(is_full, one, g_full)
+    scatter(is_causal, one, g_causal)
+    scatter(is_partial, pidx, g_pool)
+    rr = torch.arange(G, device=dev)
+    below, on_diag = rr.view(G, 1) > rr.view(1, G), rr.view(G, 1) == rr.view(1, G)
+    # a CAUSAL entry off the diagonal is all-true below it and empty above it (absolute positions)
+    full_s = (g_full | (g_causal & below)) & (g_pool < 0)
+    tril_s = g_causal & on_diag & ~g_full & (g_pool < 0)
+    part_s = g_pool >= 0
+    quad = lambda t: t.view(BH, nq, r, nq, r).permute(0, 1, 3, 2, 4).reshape(BH, nq, nq, r * r)
+    qf, qt, qp = quad(full_s), quad(tril_s), quad(part_s)
+    empty_q = ~(qf | qt | qp)
+    all_full, all_empty = qf.all(-1), empty_q.all(-1)
+    # the causal pattern of a diagonal target tile: tril on its diagonal quadrants, full below, empty above
+    a_ = torch.arange(r, device=dev)
+    want_t = (a_.view(r, 1) == a_.view(1, r)).reshape(-1)
+    want_f = (a_.view(r, 1) > a_.view(1, r)).reshape(-1)
+    tile_diag = torch.eye(nq, dtype=torch.bool, device=dev).unsqueeze(0)
+    is_c = tile_diag & (qt == want_t).all(-1) & (qf == want_f).all(-1) & ~qp.any(-1)
+    grid = torch.full((BH, nq, nq), int(BlockMaskType.PARTIAL), dtype=torch.int32, device=dev)
+    grid[is_c] = int(BlockMaskType.CAUSAL)
+    grid[all_full] = int(BlockMaskType.FULL)
+    grid[all_empty] = int(BlockMaskType.MASKED)
+    nb2, idx2, typ2 = _pack_lists(grid)
+
+    # heads whose source lists are those of their batch element's head 0 reuse its tiles
+    key = (g_full.to(torch.int64) | (g_causal.to(torch.int64) << 1) | ((g_pool + 1) << 2)).view(B, H, -1)
+    same_as_first = (key == key[:, :1]).all(-1)                       # [B, H]
+    owner = torch.where(same_as_first, torch.arange(B, device=dev).view(B, 1) * H,
+                        torch.arange(BH, device=dev).view(B, H)).reshape(BH)
+
+    is_p = (typ2 == BlockMaskType.PARTIAL) & (torch.arange(nq, device=dev) < nb2.unsqueeze(-1))
+    pidx2 = torch.full((BH, nq, nq), -1, dtype=torch.int32, device=dev)
+    pool2 = torch.empty(0, block, block, dtype=torch.bool, device=dev)
+    own = owner.view(BH, 1, 1).expand_as(is_p)
+    mine = is_p & (own == torch.arange(BH, device=dev).view(BH, 1, 1))
+    s0, s1, s2 = mine.nonzero(as_tuple=True)
+    m = s0.numel()
+    if m > 0:
+        tile_grid = torch.full((BH, nq, nq), -1, dtype=torch.long, device=dev)
+        kv = idx2[s0, s1, s2].long()
+        tile_grid[s0, s1, kv] = torch.arange(m, device=dev)
+        o0, o1, o2 = is_p.nonzero(as_tuple=True)
+        pidx2[o0, o1, o2] = tile_grid[owner[o0], o1, idx2[o0, o1, o2].long()].to(torch.int32)
+        # element masks, quadrant by quadrant
+        tril = torch.ones(src, src, dtype=torch.bool, device=dev).tril()
+        pool2 = torch.zeros(m, r, src, r, src, dtype=torch.bool, device=dev)
+        for qa in range(r):
+            for qb in range(r):
+                gi, gj = s1 * r + qa, kv * r + qb
+                f, t_, pi = full_s[s0, gi, gj], tril_s[s0, gi, gj], g_pool[s0, gi, gj]
+                tile = f.view(m, 1, 1) | (t_.view(m, 1, 1) & tril)
+                if have_pool and bool((pi >= 0).any()):
+                    from_pool = bm.partial_block_masks[pi.clamp(min=0)].to(torch.bool)
+                    tile = torch.where((pi >= 0).view(m, 1, 1), from_pool, tile)
+                pool2[:, qa, :, qb, :] = tile
+        pool2 = pool2.view(m, block, block)
+    sh = lambda t: t.view(B, H, *t.shape[1:]).contiguous()
+    out = OmniBlockMask(sh(nb2), sh(idx2), sh(typ2), n_pad, n_pad, block, block)
+    if m > 0:
+        out.partial_block_mask_indices = sh(pidx2)
+        out.partial_block_masks = pool2
+    return out
+
+
 def retile_block_mask(bm: OmniBlockMask, block: int = 128) -> OmniBlockMask:
     """The same attention pattern on another square block size.
 
     The reference's launchers accept 64x64 as well as 128x128 blocks
-    (omni-attn-mma/mma/omni_attn_shared_kv.cu:780-888); the sm_100a kernels are built for 128x128
-    only, so a 64-block mask is re-expressed here: each slice is expanded with the semantics of
-    ``dense_mask_from_blocks`` and re-derived with ``block_mask_from_dense`` (a 128x128 tile whose four
-    64x64 quadrants differ becomes PARTIAL). Heads of a batch element that share one pattern are
-    converted once. One [N, N] boolean slice is alive at a time.
+    (omni-attn-mma/mma/omni_attn_shared_kv.cu:780-888). The forward kernels take both; the backward
+    kernels and FlexAttention conversions work on 128x128, so other masks are re-expressed here. When
+    the source block size divides ``block`` (64 -> 128, the case that matters) the target tiles are
+    composed from their quadrants and nothing N x N is built. Otherwise each slice is expanded with
+    ``dense_mask_from_blocks`` and re-derived with ``block_mask_from_dense``, one [N, N] boolean
+    slice at a time (heads that share one pattern are converted once); for small sizes and tests.
     """
+    if bm.Q_BLOCK_SIZE == bm.KV_BLOCK_SIZE and block % bm.Q_BLOCK_SIZE == 0 and bm.q_len == bm.kv_len:
+        return _retile_by_quadrants(bm, block)
     B, H = bm.kv_num_blocks.shape[:2]
     n_pad = -(-max(bm.q_len, bm.kv_len) // block) * block
     parts, seen = [], {}

@@ -252,3 +252,45 @@ def test_partial_pool_can_be_left_unexpanded_until_it_is_read():
     fresh = OmniBlockMask(bm.kv_num_blocks, bm.kv_indices, bm.block_mask_types, 256, 256, 128, 128, None,
                           torch.zeros(1, 128, 128, dtype=torch.bool))
     assert fresh.partial_block_masks.shape == (1, 128, 128)
+
+
+@pytest.mark.parametrize("src,nblk", [(64, 6), (64, 5), (32, 8)])
+def test_retile_by_quadrants_expands_to_the_same_dense_mask(src, nblk):
+    """Random lists on small blocks (every type, CAUSAL entries off the diagonal, PARTIAL entries with
+    and without a pool tile, listed MASKED entries, an odd block count, heads that do and do not share
+    head 0's lists): the 128-tile mask composed from quadrants expands to the same dense mask."""
+    from omni_attention_b200.block_mask import retile_block_mask
+
+    g = torch.Generator().manual_seed(100 + nblk + src)
+    B, H = 2, 3
+    n = src * nblk
+    grid = torch.randint(0, 4, (B, H, nblk, nblk), generator=g).to(torch.int32)
+    grid[:, 1] = grid[:, 0]                      # head 1 shares head 0's lists
+    grid[0, :, 2] = 0                            # an empty row of blocks
+    order = torch.argsort(torch.rand(B, H, nblk, nblk, generator=g), dim=-1)   # lists in random order
+    listed = torch.gather(grid, -1, order) != 0
+    keep = torch.argsort((~listed).to(torch.int32), dim=-1, stable=True)
+    idx = torch.gather(order, -1, keep).to(torch.int32)
+    typ = torch.gather(grid, -1, idx.long())
+    nb = (typ != 0).sum(-1).to(torch.int32)
+    nb[1, 2, 0] = min(nblk, int(nb[1, 2, 0]) + 1)            # one listed MASKED entry
+    is_p = typ == int(BlockMaskType.PARTIAL)
+    pidx = torch.full_like(idx, -1)
+    count = int(is_p.sum())
+    pidx[is_p] = torch.arange(count, dtype=torch.int32)
+    drop = is_p & (torch.rand(B, H, nblk, nblk, generator=g) < 0.2)
+    pidx[drop] = -1                                          # PARTIAL without a tile: read as CAUSAL
+    for t in (nb, idx, typ, pidx):                           # head 1 is head 0 once more
+        t[:, 1] = t[:, 0]
+    pool = torch.rand(max(count, 1), src, src, generator=g) < 0.5
+    bm = OmniBlockMask(nb, idx, typ, n, n, src, src, pidx, pool)
+    want = dense_mask_from_blocks(bm)
+    out = retile_block_mask(bm, 128)
+    n_pad = -(-n // 128) * 128
+    assert (out.Q_BLOCK_SIZE, out.q_len, out.kv_len) == (128, n_pad, n_pad)
+    got = dense_mask_from_blocks(out)
+    assert torch.equal(got[:, :, :n, :n], want)
+    assert not bool(got[:, :, n:].any()) and not bool(got[:, :, :, n:].any())
+    if out.partial_block_masks is not None:
+        # heads 0 and 1 share their tiles
+        assert torch.equal(out.partial_block_mask_indices[:, 0], out.partial_block_mask_indices[:, 1])
