@@ -11,7 +11,7 @@ import math
 import pytest
 import torch
 
-from conftest import GOLDEN_CASES, load_golden
+from conftest import GOLDEN_CASES, GOLDEN_CASES_64_32, load_golden
 from omni_attention_b200 import (BlockMaskType, OmniBlockMask, create_causal_omni_block_mask, inputs, omni_attention,
                                  omni_attention_autograd, ops)
 from omni_attention_b200.block_mask import dense_mask_from_blocks
@@ -62,6 +62,28 @@ def test_backward_on_the_golden_cases(cuda_device, name, dtype):
     heads = all_heads(q.shape[0], q.shape[1])
     ref = orc.block_mask_attention_backward(q, k, v, g["bm"], d_out)
     assert_grads(backward(q, k, v, d_out, g["bm"], cuda_device), ref, dtype, heads, name)
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES_64_32)
+def test_autograd_op_on_64_blocks_and_head_dim_32(cuda_device, name):
+    """The differentiable operator on the reference's other block shape and head_dim: the forward takes
+    them as they are, the backward gets the mask re-tiled to 128 (quadrant by quadrant) and head_dim 32
+    zero-padded; gradients against autograd through the oracle on the original mask."""
+    g = load_golden(name)
+    dtype = torch.float16
+    q, k, v = (g[n].to(dtype) for n in ("q", "k", "v"))
+    torch.manual_seed(13)
+    d_out = torch.randn(q.shape).to(dtype)
+    heads = all_heads(q.shape[0], q.shape[1])
+    n = q.shape[2]
+    assert g["bm"].q_len == n   # the goldens are stored at the padded length
+    ref = orc.block_mask_attention_backward(q, k, v, g["bm"], d_out)
+    qd, kd, vd = (t.to(cuda_device).requires_grad_(True) for t in (q, k, v))
+    out = omni_attention_autograd(qd, kd, vd, g["bm"])
+    assert torch.equal(out.detach(), omni_attention(qd.detach(), kd.detach(), vd.detach(), g["bm"]))
+    out.backward(d_out.to(cuda_device))
+    got = tuple(t.grad.float().cpu() for t in (qd, kd, vd))
+    assert_grads(got, ref, dtype, heads, name)
 
 
 @pytest.mark.parametrize("cname,heads", [("C1", None), ("C2", None), ("C3", [(0, 0), (1, 7), (1, 15)])])
