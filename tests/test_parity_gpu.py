@@ -519,3 +519,32 @@ def test_config_c4_on_the_inputs_the_bench_times(cuda_device, seed):
     got_l = lse.cpu().view(cfg.H, cfg.N)[rb, rq]
     assert_parity(got, got_l, so, sl, f"C4 bench inputs, seed {seed}")
     assert_parity(out, lse, out_s.float(), lse_s, f"C4 bench inputs, seed {seed}: ws vs simple")
+
+
+def test_repeated_launches_give_the_same_bits(cuda_device):
+    """Which CTA draws which unit changes from launch to launch (dynamic hand-out), and the L2 state
+    with it; neither may change a bit of the result. C3 forward (with log-sum-exp) and backward, 25
+    launches each against the first one."""
+    q, k, v, bm, _ = inputs.make_inputs("C3", seed=3)
+    qd, kd, vd = (t.to(cuda_device) for t in (q, k, v))
+    first = None
+    for it in range(25):
+        out = torch.empty_like(qd)
+        lse = torch.empty(q.shape[:3], dtype=torch.float32, device=cuda_device)
+        status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+        ops.omni_attention_forward_out(qd, kd, vd, out, bm, q.shape[2], None, lse, status)
+        if first is None:
+            first = (out.clone(), lse.clone())
+            d_out = torch.randn_like(qd)
+        else:
+            assert torch.equal(out, first[0]) and torch.equal(lse, first[1]), f"forward launch {it} differs"
+        assert int(status.item()) == 0
+    grads = None
+    for it in range(25):
+        dq, dk, dv = torch.empty_like(qd), torch.empty_like(qd), torch.empty_like(qd)
+        ops.omni_attention_backward_out(qd, kd, vd, first[0], first[1], d_out, dq, dk, dv, bm, q.shape[2], None, status)
+        if grads is None:
+            grads = (dq, dk, dv)
+        else:
+            assert all(torch.equal(a, b) for a, b in zip((dq, dk, dv), grads)), f"backward launch {it} differs"
+    assert int(status.item()) == 0
