@@ -262,6 +262,45 @@ def run_ours(args, rank, local_rank, world):
         dist.barrier()
     torch.cuda.synchronize()
     clocks = sampler.stop()
+    # ---- C5 (32K multi-image), batch*heads sharded over the ranks: strong scaling, reported aside --
+    # Last on purpose: its 34 ms launches draw enough power to lower the SM clock for a while, which
+    # would otherwise be carried into the short measurements above.
+    c5 = None
+    if not args.no_c5:
+        c5cfg = inputs.CONFIGS["C5"]
+        bm5, _ = inputs.make_block_mask(c5cfg, seed=0)
+        BH = c5cfg.B * c5cfg.H
+        shard, (lo, hi) = sharding.shard_block_mask(bm5, rank, world)
+        fl5 = inputs.effective_flops(bm5, c5cfg.D)
+        q5, k5, v5 = device_qkv(1, hi - lo, c5cfg.N, c5cfg.D, c5cfg.dtype, 99 + rank, dev, c5cfg.qkv_scale)
+        o5 = torch.empty_like(q5)
+
+        def step5():
+            omni_attention_forward_out(q5, k5, v5, o5, shard, c5cfg.N, None, None, status, "ws")
+
+        step5()
+        if world > 1:
+            dist.barrier()
+        ms5 = time_steps(step5, 5, 3, flush) / 5
+        c5 = {"ms": ms5, "flops_all_ranks": fl5, "gather_ms": 0.0, "gather_bytes": 0}
+        if world > 1:
+            # optional epilogue for callers that want the whole output on every GPU: one NCCL all-gather of
+            # the ranks' own output buffers, timed on its own (not part of the forward)
+            full = sharding.all_gather_outputs(o5, BH)      # warm-up (communicator set-up)
+            del full
+            torch.cuda.synchronize()
+            dist.barrier()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            full = sharding.all_gather_outputs(o5, BH)
+            g1.record()
+            torch.cuda.synchronize()
+            assert torch.equal(full[lo:hi], o5[0]), "gathered rows of the own range differ from the local output"
+            c5["gather_ms"] = g0.elapsed_time(g1)
+            c5["gather_bytes"] = (BH - (hi - lo)) * c5cfg.N * c5cfg.D * 2
+            del full
+        del q5, k5, v5, o5
+
     if int(status.item()) != 0:
         raise RuntimeError(f"kernel status {int(status.item()):#x}")
 
@@ -340,43 +379,6 @@ def run_ours(args, rank, local_rank, world):
     fn()
     dropin_med, dropin_min = median_ms(fn, flush)
     del pool_bytes
-
-    # ---- C5 (32K multi-image), batch*heads sharded over the ranks: strong scaling, reported aside --
-    c5 = None
-    if not args.no_c5:
-        c5cfg = inputs.CONFIGS["C5"]
-        bm5, _ = inputs.make_block_mask(c5cfg, seed=0)
-        BH = c5cfg.B * c5cfg.H
-        shard, (lo, hi) = sharding.shard_block_mask(bm5, rank, world)
-        fl5 = inputs.effective_flops(bm5, c5cfg.D)
-        q5, k5, v5 = device_qkv(1, hi - lo, c5cfg.N, c5cfg.D, c5cfg.dtype, 99 + rank, dev, c5cfg.qkv_scale)
-        o5 = torch.empty_like(q5)
-
-        def step5():
-            omni_attention_forward_out(q5, k5, v5, o5, shard, c5cfg.N, None, None, status, "ws")
-
-        step5()
-        if world > 1:
-            dist.barrier()
-        ms5 = time_steps(step5, 5, 3, flush) / 5
-        c5 = {"ms": ms5, "flops_all_ranks": fl5, "gather_ms": 0.0, "gather_bytes": 0}
-        if world > 1:
-            # optional epilogue for callers that want the whole output on every GPU: one NCCL all-gather of
-            # the ranks' own output buffers, timed on its own (not part of the forward)
-            full = sharding.all_gather_outputs(o5, BH)      # warm-up (communicator set-up)
-            del full
-            torch.cuda.synchronize()
-            dist.barrier()
-            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            g0.record()
-            full = sharding.all_gather_outputs(o5, BH)
-            g1.record()
-            torch.cuda.synchronize()
-            assert torch.equal(full[lo:hi], o5[0]), "gathered rows of the own range differ from the local output"
-            c5["gather_ms"] = g0.elapsed_time(g1)
-            c5["gather_bytes"] = (BH - (hi - lo)) * c5cfg.N * c5cfg.D * 2
-            del full
-        del q5, k5, v5, o5
 
     # ---- backward pass on the same workload (three launches per step), reported aside ---------------
     bwd_ms = 0.0
