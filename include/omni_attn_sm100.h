@@ -42,7 +42,7 @@ extern "C" {
 #define OMNI_OK 0
 #define OMNI_ERR_NULL_POINTER (-1)     /* a required pointer is NULL */
 #define OMNI_ERR_DTYPE (-2)            /* dtype is neither fp16 nor bf16 */
-#define OMNI_ERR_HEAD_DIM (-3)         /* head_dim not in {32, 64, 128} (omni-attn-mma/mma/omni_attn_shared_kv.cu:725-729); the backward pass takes 64 and 128 */
+#define OMNI_ERR_HEAD_DIM (-3)         /* head_dim not in {32, 64, 128} (omni-attn-mma/mma/omni_attn_shared_kv.cu:725-729) */
 #define OMNI_ERR_BLOCK_SIZE (-4)       /* q_block/kv_block differ or are not 64 or 128 (omni_attn_shared_kv.cu:732-741); the backward pass takes 128 */
 #define OMNI_ERR_SEQLEN (-5)           /* seqlen_padded not a positive multiple of the block, or seqlen_orig outside (0, seqlen_padded] */
 #define OMNI_ERR_SHAPE (-6)            /* B, H or max_blocks not positive, or B*H > 65535 (backward pass: or B*H*seqlen >= 2^31) */
@@ -263,6 +263,8 @@ int omni_attn_build_mask_sm100(const int32_t* modality_positions, int B, int M, 
  *                      16-byte aligned; holds no state between calls, and two calls that overlap in time
  *                      need two workspaces
  * The list, pool, size, dtype, scale, stream and status arguments are those of omni_attn_fwd_sm100.
+ * head_dim 32, 64 or 128 as in the forward; the backward takes 128x128 blocks only (OMNI_ERR_BLOCK_SIZE for
+ * 64x64: re-express such a mask on 128-tiles first, as the Python operator does).
  * Three kernels are enqueued on cuda_stream; the result is deterministic (no atomics). */
 long long omni_attn_bwd_workspace_bytes(int B, int H, int seqlen_padded);
 int omni_attn_bwd_sm100(const void* q, const void* k, const void* v, const void* o, const float* lse,

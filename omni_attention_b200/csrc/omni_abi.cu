@@ -230,7 +230,7 @@ int backward(const void* q, const void* k, const void* v, const void* o, const f
     return OMNI_ERR_NULL_POINTER;
   }
   if (dtype != OMNI_DTYPE_F16 && dtype != OMNI_DTYPE_BF16) return OMNI_ERR_DTYPE;
-  if (head_dim != 64 && head_dim != 128) return OMNI_ERR_HEAD_DIM;
+  if (head_dim != 32 && head_dim != 64 && head_dim != 128) return OMNI_ERR_HEAD_DIM;
   if (q_block != kBlock || kv_block != kBlock) return OMNI_ERR_BLOCK_SIZE;
   if (seqlen_padded <= 0 || seqlen_padded % kBlock != 0 || seqlen_orig <= 0 || seqlen_orig > seqlen_padded) {
     return OMNI_ERR_SEQLEN;
@@ -302,7 +302,9 @@ int backward(const void* q, const void* k, const void* v, const void* o, const f
   p.codes = static_cast<uint32_t*>(workspace);
   p.delta = reinterpret_cast<float*>(static_cast<char*>(workspace) +
                                      ((BH * nq * nq * 4 + 255) / 256) * 256);
-  cudaError_t e = launch_bwd(head_dim, bf16, tmQ, tmK, tmV, tmdO, p, static_cast<cudaStream_t>(stream));
+  // head_dim 32 runs on the 64-wide kernels: the tensor maps' innermost extent is 32, so the TMA unit
+  // fills columns 32..63 of every tile with zeros, which changes none of the five contractions' first 32 columns
+  cudaError_t e = launch_bwd(head_dim == 32 ? 64 : head_dim, bf16, tmQ, tmK, tmV, tmdO, p, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) {
     g_last_cuda_error = static_cast<int>(e);
     return OMNI_ERR_CUDA;

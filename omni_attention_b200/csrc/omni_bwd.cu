@@ -92,15 +92,19 @@ __global__ void __launch_bounds__(128) omni_bwd_prep_kernel(const BwdParams p) {
   constexpr int kWords = D / 64;   // 32-bit words (2 elements) per lane
   for (int rr = 0; rr < 32; ++rr) {
     const long long row = static_cast<long long>(bh) * p.f.N + qb * kBlock + warp * 32 + rr;
-    const uint32_t* po = reinterpret_cast<const uint32_t*>(static_cast<const char*>(p.o) + row * (D * 2)) + lane * kWords;
-    const uint32_t* pd = reinterpret_cast<const uint32_t*>(static_cast<const char*>(p.d_o) + row * (D * 2)) + lane * kWords;
+    // rows are d_real elements long (head_dim 32 runs on the 64-wide instantiation: the upper lanes idle)
+    const long long pitch = static_cast<long long>(p.f.d_real) * 2;
+    const uint32_t* po = reinterpret_cast<const uint32_t*>(static_cast<const char*>(p.o) + row * pitch) + lane * kWords;
+    const uint32_t* pd = reinterpret_cast<const uint32_t*>(static_cast<const char*>(p.d_o) + row * pitch) + lane * kWords;
     float acc = 0.f;
+    if (lane * kWords * 2 < p.f.d_real) {
 #pragma unroll
-    for (int w = 0; w < kWords; ++w) {
-      const float2 a = unpack2<BF16>(__ldg(po + w));
-      const float2 b = unpack2<BF16>(__ldg(pd + w));
-      acc = fmaf(a.x, b.x, acc);
-      acc = fmaf(a.y, b.y, acc);
+      for (int w = 0; w < kWords; ++w) {
+        const float2 a = unpack2<BF16>(__ldg(po + w));
+        const float2 b = unpack2<BF16>(__ldg(pd + w));
+        acc = fmaf(a.x, b.x, acc);
+        acc = fmaf(a.y, b.y, acc);
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
@@ -166,10 +170,13 @@ __device__ __forceinline__ void bwd_mma_ts_split(uint32_t d_tmem, uint32_t a_reg
 // 16-bit values to global memory (zeros when `have_acc` is false).
 template <int D, bool BF16, int kFirstChunk = 0, int kEndChunk = D / 32>
 __device__ __forceinline__ void bwd_store_row(uint32_t taddr_row, bool have_acc, float mul, void* base,
-                                              long long row_index) {
-  uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(base) + row_index * (D * 2));
+                                              long long row_index, int d_real) {
+  // rows of the output are d_real elements long; accumulator columns beyond that (head_dim 32 on the
+  // 64-wide instantiation) are zero and are not stored
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(base) + row_index * (static_cast<long long>(d_real) * 2));
 #pragma unroll
   for (int c = kFirstChunk; c < kEndChunk; ++c) {
+    if (32 * c >= d_real) break;
     uint32_t r[32];
     if (have_acc) {
       tmem_ld32(taddr_row + 32 * c, r);
@@ -573,9 +580,9 @@ omni_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     const long long out_row = row0 + k_abs;
     if (half == 0) {
-      bwd_store_row<D, BF16>(tdV + lane_base, n_vis > 0, 1.f, p.dv, out_row);
+      bwd_store_row<D, BF16>(tdV + lane_base, n_vis > 0, 1.f, p.dv, out_row, p.f.d_real);
     } else {
-      bwd_store_row<D, BF16>(tdK + lane_base, n_vis > 0, p.f.scale, p.dk, out_row);
+      bwd_store_row<D, BF16>(tdK + lane_base, n_vis > 0, p.f.scale, p.dk, out_row, p.f.d_real);
     }
   }
 
@@ -836,9 +843,9 @@ omni_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
     }
     if (half == 0) {
-      bwd_store_row<D, BF16, 0, D / 64>(tdQ + lane_base, n_vis > 0, p.f.scale, p.dq, my_row);
+      bwd_store_row<D, BF16, 0, D / 64>(tdQ + lane_base, n_vis > 0, p.f.scale, p.dq, my_row, p.f.d_real);
     } else {
-      bwd_store_row<D, BF16, D / 64, D / 32>(tdQ + lane_base, n_vis > 0, p.f.scale, p.dq, my_row);
+      bwd_store_row<D, BF16, D / 64, D / 32>(tdQ + lane_base, n_vis > 0, p.f.scale, p.dq, my_row, p.f.d_real);
     }
   }
 

@@ -297,10 +297,8 @@ def _prepare(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMas
     so all that happens here is the reference wrapper's zero-padding of the sequence to a multiple of
     the mask's block size (omni_attn_torch.py:1261-1284).
 
-    The backward kernels are built for head_dim 64/128 and 128x128 blocks only; with ``for_backward``
-    the other two forms are mapped onto those on the host: a 64x64-block mask is re-tiled to 128x128
-    once (cached on the mask object) and head_dim 32 is zero-padded to 64 with the scale kept at
-    1/sqrt(32) - zero columns change neither Q K^T nor the first 32 output columns.
+    The backward kernels take 128x128 blocks only; with ``for_backward`` a 64x64-block mask is
+    re-expressed on 128-tiles once (quadrant by quadrant, cached on the mask object).
     Returns padded contiguous q, k, v, the mask to use, the scale, and the original length / head_dim."""
     B, H, Q, D = query.shape
     if key.shape != (B, H, Q, D) or value.shape != (B, H, Q, D):
@@ -319,10 +317,6 @@ def _prepare(query: Tensor, key: Tensor, value: Tensor, block_mask: OmniBlockMas
                 hit = retile_block_mask(block_mask, 128)
                 block_mask._cache["retiled128"] = hit
             block_mask = hit
-        if D == 32:
-            if scale is None:
-                scale = 1.0 / math.sqrt(32)
-            query, key, value = (torch.nn.functional.pad(t, (0, 32)) for t in (query, key, value))
     blk = block_mask.Q_BLOCK_SIZE
     qp, n_orig = _pad_to_block(query, blk)
     kp, _ = _pad_to_block(key, blk)

@@ -164,7 +164,8 @@ def test_backward_argument_validation_codes(fn):
     for name in ("q", "lse", "do", "dq", "dk", "dv", "typ", "ws"):
         assert _call_bwd(lib, fn, **{name: None}) == E["OMNI_ERR_NULL_POINTER"], name
     assert _call_bwd(lib, fn, dtype=3) == E["OMNI_ERR_DTYPE"]
-    assert _call_bwd(lib, fn, D=32) == E["OMNI_ERR_HEAD_DIM"]
+    assert _call_bwd(lib, fn, D=48) == E["OMNI_ERR_HEAD_DIM"]
+    assert _call_bwd(lib, fn, D=256) == E["OMNI_ERR_HEAD_DIM"]
     assert _call_bwd(lib, fn, qb=64, kb=64) == E["OMNI_ERR_BLOCK_SIZE"]
     assert _call_bwd(lib, fn, N=130) == E["OMNI_ERR_SEQLEN"]
     assert _call_bwd(lib, fn, orig=200) == E["OMNI_ERR_SEQLEN"]
