@@ -16,7 +16,7 @@ import torch
 
 from conftest import GOLDEN_CASES_64_32, GOLDEN_DIR, LSE_ATOL, ROOT, assert_parity, load_golden
 from omni_attention_b200 import ops
-from omni_attention_b200.block_mask import BlockMaskType, OmniBlockMask, retile_block_mask
+from omni_attention_b200.block_mask import BlockMaskType, OmniBlockMask, dense_mask_from_blocks, retile_block_mask
 from omni_attention_b200.ops import omni_attention
 from oracle import omni_oracle as orc
 
@@ -292,3 +292,81 @@ def test_a_wait_that_runs_out_is_reported_and_the_next_call_is_right(cuda_device
             lib.omni_attn_set_wait_cycles(0)
     good, lse = run(g["q"], g["k"], g["v"], g["bm"], dev)
     assert_parity(good, lse, g["out"], g["lse"], "call after a timed-out one")
+
+
+def _random_case(seed):
+    """A small random mask and inputs: either block size, any head_dim and dtype, lists in random order
+    with every type (MASKED entries, PARTIAL entries with and without a pool tile), garbage behind the
+    list ends, sometimes a ragged length."""
+    import random
+
+    rnd = random.Random(seed)
+    g = torch.Generator().manual_seed(seed)
+    blk = rnd.choice([64, 128])
+    nblk = rnd.randint(1, 9 if blk == 64 else 5)
+    D = rnd.choice([32, 64, 128])
+    dtype = rnd.choice([torch.float16, torch.bfloat16])
+    B, H = rnd.choice([1, 2]), rnd.choice([1, 3])
+    N = blk * nblk
+    n_orig = rnd.choice([N, N, rnd.randint(N - blk + 1, N)])
+    mb = nblk + rnd.choice([0, 0, 2])
+    nb = torch.zeros(B, H, nblk, dtype=torch.int32)
+    idx = torch.zeros(B, H, nblk, mb, dtype=torch.int32)
+    typ = torch.zeros_like(idx)
+    pidx = torch.full_like(idx, -1)
+    pools = []
+    for b in range(B):
+        for h in range(H):
+            for qb in range(nblk):
+                ks = [kb for kb in range(nblk) if rnd.random() < 0.6]
+                rnd.shuffle(ks)
+                nb[b, h, qb] = len(ks)
+                for i, kb in enumerate(ks):
+                    t = rnd.choice([0, 1, 2, 2, 3, 3])
+                    idx[b, h, qb, i], typ[b, h, qb, i] = kb, t
+                    if t == 3 and rnd.random() < 0.85:
+                        pidx[b, h, qb, i] = len(pools)
+                        pools.append(torch.rand(blk, blk, generator=g) < rnd.choice([0.05, 0.5, 0.95]))
+                for i in range(len(ks), mb):
+                    idx[b, h, qb, i], typ[b, h, qb, i] = rnd.randint(0, nblk - 1), rnd.choice([0, 1, 2, 3])
+    pool = torch.stack(pools) if pools else None
+    bm = OmniBlockMask(nb, idx, typ, N, N, blk, blk, pidx if pool is not None else None, pool)
+    q, k, v, d_out = (torch.randn(B, H, n_orig, D, generator=g).to(dtype) for _ in range(4))
+    return bm, q, k, v, d_out, N, n_orig, dtype
+
+
+@pytest.mark.parametrize("chunk", range(4))
+def test_random_small_masks_forward_and_dv(cuda_device, chunk):
+    """15 random cases per chunk: both kernels against the oracle on every row that may attend a key
+    (exact zeros and -inf on the others), and dV of the differentiable operator (dV does not depend on
+    the rounded output the way dQ and dK do through delta; those two are checked to be finite and within
+    4x the tolerance of tests/test_backward_gpu.py)."""
+    from omni_attention_b200 import omni_attention_autograd
+
+    for case in range(15):
+        seed = 7000 + 100 * chunk + case
+        bm, q, k, v, d_out, N, n_orig, dtype = _random_case(seed)
+        pad = lambda t: torch.nn.functional.pad(t, (0, 0, 0, N - n_orig))
+        ref_o, ref_l = orc.block_mask_attention(pad(q), pad(k), pad(v), bm, seqlen_orig=n_orig)
+        dense = dense_mask_from_blocks(bm).clone()
+        dense[..., n_orig:] = False
+        live = dense.any(-1)[:, :, :n_orig]
+        for kernel in KERNELS:
+            out, lse = run(q, k, v, bm, cuda_device, kernel)
+            out, lse = out.float().cpu(), lse.cpu()
+            assert bool((out[~live] == 0).all()) and bool(torch.isinf(lse[~live]).all()), f"seed {seed} {kernel}: dead rows"
+            if bool(live.any()):
+                assert_parity(out[live], lse[live], ref_o[:, :, :n_orig][live], ref_l[:, :, :n_orig][live], f"seed {seed} {kernel}")
+        qd, kd, vd = (t.to(cuda_device).requires_grad_(True) for t in (q, k, v))
+        omni_attention_autograd(qd, kd, vd, bm).backward(d_out.to(cuda_device))
+        ref = orc.block_mask_attention_backward(pad(q), pad(k), pad(v), bm, pad(d_out), seqlen_orig=n_orig)
+        rt = 4e-3 if dtype == torch.float16 else 2e-2
+        for name, got, r, slack in (("dq", qd.grad, ref[0], 4.0), ("dk", kd.grad, ref[1], 4.0), ("dv", vd.grad, ref[2], 1.0)):
+            got, r = got.float().cpu(), r[:, :, :n_orig]
+            assert bool(torch.isfinite(got).all()), f"seed {seed} {name}"
+            for b in range(q.shape[0]):
+                for h in range(q.shape[1]):
+                    scale_ = float(r[b, h].abs().max())
+                    if scale_ > 0.05:   # heads whose true gradient is (almost) zero have no relative tolerance
+                        err = float((got[b, h] - r[b, h]).abs().max())
+                        assert err <= slack * rt * scale_, f"seed {seed} {name}[{b},{h}]: {err:.3g} > {slack * rt * scale_:.3g}"
