@@ -83,11 +83,13 @@ def test_config_c4_sampled_heads_and_rows(cuda_device):
     assert_parity(out, lse, out_s.float(), lse_s, "C4 ws vs simple")
 
 
-def test_config_c5_shape_sharded_slice(cuda_device):
-    """The 32K multi-image configuration, the shard one of 8 GPUs would own (16 of the 128
-    batch*head pairs), checked on sampled rows and through properties that need no oracle."""
+@pytest.mark.parametrize("lo", [0, 48, 112])
+def test_config_c5_shape_sharded_slice(cuda_device, lo):
+    """The 32K multi-image configuration, a shard one of 8 GPUs would own (16 of the 128
+    batch*head pairs; the first, a middle and the last one), checked on sampled rows and through
+    properties that need no oracle."""
     cfg = inputs.CONFIGS["C5"]
-    lo, hi = 48, 64  # batch element 1, heads 16..31
+    hi = lo + 16
     q, k, v, bm, _ = inputs.make_inputs("C5", seed=0, bh_range=(lo, hi))
     out, lse = run(q, k, v, bm, cuda_device)
     assert out.shape == (1, hi - lo, cfg.N, cfg.D)
