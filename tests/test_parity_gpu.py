@@ -83,11 +83,10 @@ def test_config_c4_sampled_heads_and_rows(cuda_device):
     assert_parity(out, lse, out_s.float(), lse_s, "C4 ws vs simple")
 
 
-@pytest.mark.parametrize("lo", [0, 48, 112])
+@pytest.mark.parametrize("lo", list(range(0, 128, 16)))
 def test_config_c5_shape_sharded_slice(cuda_device, lo):
-    """The 32K multi-image configuration, a shard one of 8 GPUs would own (16 of the 128
-    batch*head pairs; the first, a middle and the last one), checked on sampled rows and through
-    properties that need no oracle."""
+    """The 32K multi-image configuration, shard by shard as 8 GPUs would own it (16 of the 128
+    batch*head pairs each), checked on sampled rows and through properties that need no oracle."""
     cfg = inputs.CONFIGS["C5"]
     hi = lo + 16
     q, k, v, bm, _ = inputs.make_inputs("C5", seed=0, bh_range=(lo, hi))
