@@ -15,7 +15,7 @@ Timing: W warm-up steps, then K steps each bracketed by CUDA events on the launc
 host->device copies of q, k, v and the device->host copy of the output inside the timed region;
 `e2e.copy_only` is the same copy pattern with no kernel (the floor the host link sets).
 Reported aside in the same line: the other configurations (`configs`), the reference's 13-argument
-module entry (`dropin_13arg`), the 32K configuration sharded over the ranks with its optional
+module entry (`dropin_13arg`), the same mask listed in 64x64 blocks (`blocks_64x64`), the 32K configuration sharded over the ranks with its optional
 all-gather (`c5_sharded`), the backward pass and the soft-cap variant.
 `--impl reference` times the reference's CPU torch path (the oracle's restatement of
 omni_attn_torch.naive_attention_with_dense_mask, the additive mask of a head built beforehand) on
@@ -240,7 +240,7 @@ def run_ours(args, rank, local_rank, world):
     torch.cuda.set_device(dev)
     peak_tf, peak_hbm, which = measured_peaks()
     # one batch element per rank; every rank draws its own image/text layout
-    bm, _ = inputs.make_block_mask(cfg, seed=rank, B=1)
+    bm, mask_meta = inputs.make_block_mask(cfg, seed=rank, B=1)
     flops = inputs.effective_flops(bm, cfg.D)
     q, k, v = device_qkv(1, cfg.H, cfg.N, cfg.D, cfg.dtype, 1234 + rank, dev, cfg.qkv_scale)
     out = torch.empty_like(q)
@@ -380,6 +380,20 @@ def run_ours(args, rank, local_rank, world):
     dropin_med, dropin_min = median_ms(fn, flush)
     del pool_bytes
 
+    # ---- the same pattern listed in 64x64 blocks (the reference's other block shape), reported aside ----
+    from omni_attention_b200.block_mask import block_mask_from_row_limits, row_limits_from_modality_positions
+
+    limits64, causal_rows64 = row_limits_from_modality_positions(cfg.N, mask_meta["image_spans"])
+    bm64 = block_mask_from_row_limits(limits64, cfg.H, causal_rows64, 64, True)
+    out64 = torch.empty_like(out)
+    fn64 = lambda: omni_attention_forward_out(q, k, v, out64, bm64, cfg.N, None, None, status, "ws")
+    fn64()
+    blk64_med, blk64_min = median_ms(fn64, flush)
+    step()
+    torch.cuda.synchronize()
+    blk64_same = bool(torch.equal(out64, out))
+    del out64
+
     # ---- backward pass on the same workload (three launches per step), reported aside ---------------
     bwd_ms = 0.0
     if not args.no_backward:
@@ -455,6 +469,10 @@ def run_ours(args, rank, local_rank, world):
         "gpu_launches": args.steps,
         "clocks": clocks,
         "configs": configs,
+        "blocks_64x64": {"ms": blk64_med, "ms_min": blk64_min, "tflops": flops / blk64_med / 1e9,
+                         "over_headline": blk64_med / ms_per_step, "listed_blocks": int(bm64.visited_blocks()),
+                         "bit_identical_to_128_blocks": blk64_same,
+                         "what": "the same mask listed in 64x64 blocks (four times as many entries), same kernel"},
         "dropin_13arg": {"ms": dropin_med, "ms_min": dropin_min, "tflops": flops / dropin_med / 1e9,
                          "over_headline": dropin_med / ms_per_step,
                          "what": "omni_attn.omni_attn_mma_stages_split_q_shared_kv(13 positional arguments) on the same inputs: "

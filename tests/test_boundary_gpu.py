@@ -370,3 +370,21 @@ def test_random_small_masks_forward_and_dv(cuda_device, chunk):
                     if scale_ > 0.05:   # heads whose true gradient is (almost) zero have no relative tolerance
                         err = float((got[b, h] - r[b, h]).abs().max())
                         assert err <= slack * rt * scale_, f"seed {seed} {name}[{b},{h}]: {err:.3g} > {slack * rt * scale_:.3g}"
+
+
+def test_c3_pattern_listed_in_64_blocks_gives_the_same_bits(cuda_device):
+    """The interleaved 4K-token workload listed in 64x64 blocks (four times as many entries, PARTIAL
+    tiles of 64x64) against the same pattern in 128x128 blocks: same kernel, same allow bits, same bits
+    out, on both kernels."""
+    from omni_attention_b200 import inputs
+    from omni_attention_b200.block_mask import block_mask_from_row_limits, row_limits_from_modality_positions
+
+    cfg = inputs.CONFIGS["C3"]
+    q, k, v, bm128, meta = inputs.make_inputs("C3", seed=2)
+    limits, causal_rows = row_limits_from_modality_positions(cfg.N, meta["image_spans"])
+    bm64 = block_mask_from_row_limits(limits, cfg.H, causal_rows, 64, True)
+    assert bm64.Q_BLOCK_SIZE == 64 and bm64.visited_blocks() > 3 * bm128.visited_blocks()
+    for kernel in ("ws", "simple"):
+        o128, l128 = run(q, k, v, bm128, cuda_device, kernel)
+        o64, l64 = run(q, k, v, bm64, cuda_device, kernel)
+        assert torch.equal(o128, o64) and torch.equal(l128, l64), kernel
